@@ -1,0 +1,437 @@
+"""The engine: model, cache, step function, scheduler and sampler in one object.
+
+Start-up order follows the reference (src/engine/engine.rs:212-248): validate
+what the configuration alone can refuse, build the model, load the weights,
+size and allocate the cache from the memory that is left, then (optionally)
+capture decode graphs.
+
+``step`` is the one step function: a batch of (request, its next tokens),
+portions of prompts beside single decoded tokens, cut anywhere.  It runs only
+the tokens it is given, from the cache that earlier steps left, and returns the
+logits at the wanted places.  Trace replay, ``generate`` and the scheduler loop
+all go through it.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import architectures  # noqa: F401  (registers the shipped architectures)
+from ..cache import PagedCache, cache_budget_bytes, plan_cache, size_groups
+from ..config.registry import resolve_architecture
+from ..config.spec import ConfigError
+from ..kernels import ops
+from ..kernels.build import load_host_runtime
+from ..parts import DecoderModel
+from ..sampling import Sampler, SamplingParams
+from ..weights.loader import load_weights, read_config_json
+from .context import StepContext
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclass
+class StepEntry:
+    """One row of a step: a live request, its next tokens, and the places (indices
+    into ``tokens``) whose logits are wanted."""
+    request: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int]
+    finish_reason: str
+
+
+def auto_chunked_prefill_size(memory_mib: int) -> int:
+    """Chunk budget by GPU memory (reference: src/engine/engine.rs:600-610)."""
+    if memory_mib < 20 * 1024:
+        return 2048
+    if memory_mib < 60 * 1024:
+        return 4096
+    if memory_mib < 160 * 1024:
+        return 8192
+    return 16384
+
+
+def graph_batch_sizes(limit: int) -> List[int]:
+    """Decode graph buckets: powers of two up to 256 that fit, and the limit itself
+    (reference: src/engine/graph.rs:93-97)."""
+    sizes = [s for s in (1, 2, 4, 8, 16, 32, 64, 128, 256) if s <= limit]
+    if limit > 0 and limit not in sizes:
+        sizes.append(limit)
+    return sorted(sizes)
+
+
+class _MetaBuffers:
+    """Pinned staging buffers (a small ring) and the device copy of a step's index arrays."""
+
+    def __init__(self, device: torch.device, ring: int = 4):
+        self.device = device
+        self.ring = ring
+        self.capacity = 0
+        self.pinned: List[torch.Tensor] = []
+        self.events: List[Optional[torch.cuda.Event]] = []
+        self.dev: Optional[torch.Tensor] = None
+        self.turn = 0
+
+    def reserve(self, ints: int) -> None:
+        if ints <= self.capacity:
+            return
+        torch.cuda.synchronize(self.device)
+        self.capacity = max(ints, 2 * self.capacity, 4096)
+        self.pinned = [torch.empty(self.capacity, dtype=torch.int32).pin_memory() for _ in range(self.ring)]
+        self.events = [None] * self.ring
+        self.dev = torch.empty(self.capacity, dtype=torch.int32, device=self.device)
+
+    def next_host(self) -> Tuple[int, torch.Tensor]:
+        self.turn = (self.turn + 1) % self.ring
+        ev = self.events[self.turn]
+        if ev is not None:
+            ev.synchronize()
+        return self.turn, self.pinned[self.turn]
+
+    def upload(self, turn: int, ints: int, dst: Optional[torch.Tensor] = None) -> torch.Tensor:
+        dst = self.dev if dst is None else dst
+        dst[:ints].copy_(self.pinned[turn][:ints], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[turn] = ev
+        return dst
+
+
+class _DecodeGraph:
+    def __init__(self, bucket: int):
+        self.bucket = bucket
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.meta: Optional[torch.Tensor] = None
+        self.ctx: Optional[StepContext] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.layout_key = None
+
+
+class Engine:
+    def __init__(self, model_path: str, *, dtype: str = "auto", device: str = "cuda",
+                 max_running_req: int = 256, max_seq_len: Optional[int] = None, page_size: int = 16,
+                 memory_ratio: float = 0.9, max_total_tokens: Optional[int] = None,
+                 max_prefill_tokens_per_batch: int = 8192, chunked_prefill_size: Optional[int] = None,
+                 cuda_graph_bs: Optional[int] = 0, eos_token_ids: Optional[Sequence[int]] = None,
+                 seed: int = 0, log_level: str = "info"):
+        self.model_path = model_path
+        self.log_level = log_level
+        raw = read_config_json(model_path)
+        self.arch = resolve_architecture(raw)
+        self.config = self.arch.parse_config(raw)
+        self.raw_config = raw
+        spec = self.arch.model_spec(self.config)
+
+        self._setup_device(device)
+        if dtype == "auto":
+            dtype = getattr(self.config, "checkpoint_dtype", "bfloat16")
+            dtype = "bfloat16" if dtype == "float16" else dtype
+        if dtype not in _DTYPES:
+            raise ConfigError(f"dtype {dtype!r} is refused: bfloat16 and float32 are supported")
+        self.dtype = _DTYPES[dtype]
+        if page_size <= 0:
+            raise ConfigError("page_size must be positive")
+        if max_running_req <= 0:
+            raise ConfigError("max_running_req must be positive")
+        if max_seq_len is None:
+            max_seq_len = min(8192, spec.max_positions)
+        if max_seq_len <= 0 or max_seq_len > spec.max_positions:
+            raise ConfigError(f"--max-seq-len {max_seq_len} exceeds the model's max_position_embeddings="
+                              f"{spec.max_positions}; lower --max-seq-len")
+        self.max_seq_len = max_seq_len
+        self.max_running_req = max_running_req
+        self.page_size = page_size
+        self.seed = seed
+
+        if chunked_prefill_size is None:
+            chunked_prefill_size = auto_chunked_prefill_size(self._total_memory_mib)
+        budgets = [b for b in (max_prefill_tokens_per_batch, chunked_prefill_size) if b and b > 0]
+        self.max_batch_tokens = min(budgets) if budgets else 0
+
+        # The true 32-bit path must not be served by a reduced-precision matrix mode.
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+
+        self.model = DecoderModel(spec, self.dtype, self.device)
+        self.loaded_tensors = load_weights(self.model, self.arch.weight_plan(self.config), model_path,
+                                           self.dtype, self.device)
+        unbound = self.model.unbound_parameters()
+        if unbound:
+            raise RuntimeError(f"the weight plan of {self.arch.name} left parameters unbound: {unbound}")
+
+        itemsize = torch.empty(0, dtype=self.dtype).element_size()
+        self.cache_plan = plan_cache(self.model, page_size, itemsize)
+        free, total = self._free_and_total_memory()
+        budget = cache_budget_bytes(free, total, memory_ratio)
+        step_bound = self.max_batch_tokens if self.max_batch_tokens > 0 else max_seq_len
+        size_groups(self.cache_plan, budget, max_total_tokens, max_running_req, max_seq_len, step_bound)
+        self.cache = PagedCache(self.model, self.cache_plan, max_running_req, self.dtype, self.device)
+        self.table_width = [-(-max_seq_len // g.page_size) for g in self.cache_plan.groups]
+
+        rt = load_host_runtime()
+        self._rt = rt
+        if eos_token_ids is None:
+            eos_token_ids = getattr(self.config, "eos_token_ids", ())
+        self.eos_token_ids = tuple(eos_token_ids)
+        self.scheduler = rt.Scheduler(self.cache.manager,
+                                      rt.SchedulerOptions(max_running_req, max_seq_len, self.max_batch_tokens),
+                                      list(self.eos_token_ids))
+        self.sampler = Sampler(self.device)
+        self._meta = self._new_meta_buffers()
+        self._scratch: Optional[torch.Tensor] = None
+        self._params: Dict[int, SamplingParams] = {}
+        self._seeds: Dict[int, int] = {}
+        self.kernel_launches = 0
+
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        if cuda_graph_bs is None:
+            cuda_graph_bs = max_running_req
+        self.cuda_graph_bs = min(int(cuda_graph_bs), max_running_req) if self.dtype == torch.bfloat16 else 0
+        for bucket in graph_batch_sizes(self.cuda_graph_bs):
+            self._graphs[bucket] = _DecodeGraph(bucket)
+
+    # ------------------------------------------------------------------ the device
+    def _setup_device(self, device: str) -> None:
+        if device not in ("cuda", "auto") and not str(device).startswith("cuda"):
+            raise ConfigError(f"device {device!r} is refused: this engine runs on CUDA only")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is visible; this engine has no CPU path")
+        self.device = torch.device("cuda:0" if device in ("cuda", "auto") else device)
+        torch.cuda.set_device(self.device)
+        props = torch.cuda.get_device_properties(self.device)
+        self.sm_count = props.multi_processor_count
+        self._total_memory_mib = props.total_memory // (1 << 20)
+
+    def _free_and_total_memory(self) -> Tuple[int, int]:
+        torch.cuda.synchronize(self.device)
+        return torch.cuda.mem_get_info(self.device)
+
+    def _new_meta_buffers(self) -> "_MetaBuffers":
+        return _MetaBuffers(self.device)
+
+    # ------------------------------------------------------------------ requests of the step function
+    def open_request(self, request: int) -> None:
+        """Make ``request`` live without a promise of pages (pages are taken as it grows)."""
+        got = self.cache.manager.open(request)
+        if got != self._rt.Acquire.Ready:
+            raise RuntimeError(f"request {request} cannot be opened: {got.name}")
+
+    def close_request(self, request: int) -> None:
+        """Give back everything ``request`` holds."""
+        self.cache.manager.release(request)
+
+    def request_length(self, request: int) -> int:
+        return self.cache.manager.length(request)
+
+    # ------------------------------------------------------------------ the step function
+    def _get_scratch(self, floats: int) -> torch.Tensor:
+        if self._scratch is None or self._scratch.numel() < floats:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("scratch memory must be sized before a graph is captured")
+            self._scratch = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=self.device)
+        return self._scratch
+
+    def _context(self, layout, dev: torch.Tensor, host: Optional[torch.Tensor], kv_len_bound: int) -> StepContext:
+        def view(off, n):
+            return dev[off:off + n]
+
+        groups = len(self.cache.page_sizes)
+        T, R = layout.num_tokens, layout.num_rows
+        return StepContext(
+            device=self.device, dtype=self.dtype, num_tokens=T, num_rows=R, num_decode=layout.num_decode,
+            num_prefill=layout.num_prefill, num_logits=layout.num_logits, max_q_len=layout.max_q_len,
+            max_kv_len=layout.max_kv_len,
+            token_ids=view(layout.off_tokens, T), positions=view(layout.off_positions, T),
+            row_of_token=view(layout.off_row_of_token, T), cu_q=view(layout.off_cu_q, R + 1),
+            kv_len=view(layout.off_kv_len, R), prefix_len=view(layout.off_prefix_len, R),
+            state_slots=view(layout.off_state_slot, R),
+            decode_rows=view(layout.off_decode_rows, layout.num_decode),
+            prefill_rows=view(layout.off_prefill_rows, layout.num_prefill),
+            logit_rows=view(layout.off_logit_rows, layout.num_logits),
+            slots=[view(layout.off_slots[g], T) for g in range(groups)],
+            block_tables=[view(layout.off_table[g], R * layout.table_width[g]).view(R, layout.table_width[g])
+                          for g in range(groups)],
+            page_sizes=list(self.cache.page_sizes),
+            host=None if host is None else host.numpy(), layout=layout, kv_len_bound=kv_len_bound,
+            scratch=self._get_scratch, sm_count=self.sm_count)
+
+    def _batch_request(self, entries: Sequence[StepEntry]):
+        req = self._rt.BatchRequest()
+        req.ids = [int(e.request) for e in entries]
+        req.counts = [len(e.tokens) for e in entries]
+        req.tokens = [int(t) for e in entries for t in e.tokens]
+        req.want_counts = [len(e.want) for e in entries]
+        req.want_index = [int(i) for e in entries for i in e.want]
+        return req
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; float32 logits [wanted, vocab] in the order of the entries and their ``want``.
+
+        The tensor may be overwritten by the next step; copy it if it must outlive that.
+        """
+        if not entries:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+        mgr = self.cache.manager
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise ValueError("a step entry must bring at least one token")
+            new_len = mgr.length(e.request) + len(e.tokens)
+            if new_len > self.model.spec.max_positions:
+                raise ValueError(f"request {e.request} would reach {new_len} tokens, beyond the model's "
+                                 f"{self.model.spec.max_positions} positions")
+            if not mgr.grow(e.request, new_len):
+                raise MemoryError(f"the cache has no pages left for request {e.request} "
+                                  f"({new_len} tokens); free pages per group: "
+                                  f"{[mgr.free_pages(g) for g in range(mgr.num_groups())]}")
+        req = self._batch_request(entries)
+        decode_only = all(c == 1 for c in req.counts)
+        graph = None
+        if decode_only and self._graphs and all(len(e.want) == 1 for e in entries):
+            bucket = next((b for b in sorted(self._graphs) if b >= len(entries)), None)
+            if bucket is not None and max(mgr.length(e.request) for e in entries) < self.max_seq_len:
+                graph = self._graphs[bucket]
+        if graph is not None:
+            logits = self._step_graph(graph, req, len(entries))
+        else:
+            logits = self._step_eager(req)
+        for e in entries:
+            mgr.advance(e.request, mgr.length(e.request) + len(e.tokens))
+        return logits
+
+    def _step_eager(self, req) -> torch.Tensor:
+        layout = self._rt.plan_batch(self.cache.manager, req)
+        self._meta.reserve(layout.total_ints)
+        turn, host = self._meta.next_host()
+        layout = self._rt.build_batch(self.cache.manager, req, host.numpy())
+        dev = self._meta.upload(turn, layout.total_ints)
+        ctx = self._context(layout, dev, host, layout.max_kv_len)
+        return self.model.forward(ctx, self.cache.layer_caches)
+
+    def _step_graph(self, g: _DecodeGraph, req, real_rows: int) -> torch.Tensor:
+        req.pad_rows_to = g.bucket
+        req.fixed_table_width = list(self.table_width)
+        layout = self._rt.plan_batch(self.cache.manager, req)
+        self._meta.reserve(layout.total_ints)
+        turn, host = self._meta.next_host()
+        layout = self._rt.build_batch(self.cache.manager, req, host.numpy())
+        if g.graph is None:
+            g.meta = torch.empty(layout.total_ints, dtype=torch.int32, device=self.device)
+            self._meta.upload(turn, layout.total_ints, g.meta)
+            g.ctx = self._context(layout, g.meta, None, self.max_seq_len)
+            # Warm up outside the capture (sizes scratch, loads kernels), then capture.
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.model.forward(g.ctx, self.cache.layer_caches)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            g.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g.graph):
+                g.logits = self.model.forward(g.ctx, self.cache.layer_caches)
+            g.layout_key = layout.total_ints
+        elif layout.total_ints != g.layout_key:
+            raise RuntimeError("a decode graph was given a batch of another shape than it was captured for")
+        self._meta.upload(turn, layout.total_ints, g.meta)
+        g.graph.replay()
+        return g.logits[:real_rows]
+
+    def capture_graphs(self) -> None:
+        """Capture every decode graph bucket now (else each is captured at its first use)."""
+        for bucket, g in sorted(self._graphs.items()):
+            if g.graph is not None:
+                continue
+            ids = [-(i + 1) for i in range(bucket)]
+            for rid in ids:
+                self.open_request(rid)
+            try:
+                entries = [StepEntry(rid, [0], [0]) for rid in ids]
+                for e in entries:
+                    if not self.cache.manager.grow(e.request, 1):
+                        raise MemoryError("not enough pages to capture the decode graphs")
+                self._step_graph(g, self._batch_request(entries), bucket)
+                torch.cuda.synchronize(self.device)
+            finally:
+                for rid in ids:
+                    self.close_request(rid)
+
+    def check_kernel_errors(self) -> None:
+        ops.check_errors(self.device)
+
+    # ------------------------------------------------------------------ scheduler loop
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = (params or SamplingParams()).normalized()
+        rt = self._rt
+        uid = self.scheduler.add_request([int(t) for t in prompt],
+                                         rt.SamplingParams(params.temperature, params.top_k, params.top_p,
+                                                           params.ignore_eos, params.max_tokens,
+                                                           (params.seed or 0) & ((1 << 64) - 1)))
+        self._params[uid] = params
+        self._seeds[uid] = params.seed if params.seed is not None else \
+            (self.seed * 0x9E3779B97F4A7C15 + uid * 0xD1B54A32D192ED03) & ((1 << 64) - 1)
+        return uid
+
+    def abort_request(self, uid: int) -> bool:
+        return self.scheduler.abort_request(uid)
+
+    def is_idle(self) -> bool:
+        return self.scheduler.is_idle()
+
+    def schedule_step(self):
+        """One scheduler step: plan, run, sample, commit.  Returns the step's output tokens."""
+        sched = self.scheduler
+        out = list(sched.drain_outbox())
+        plan = sched.plan_step()
+        out += sched.drain_outbox()
+        if not plan.entries:
+            return out
+        try:
+            entries, rows = [], []
+            for e in plan.entries:
+                entries.append(StepEntry(e.uid, sched.tokens_of(e), [e.count - 1] if e.sample else []))
+                if e.sample:
+                    rows.append((self._params[e.uid], self._seeds[e.uid], e.output_index))
+            logits = self.step(entries)
+            sampled = self.sampler.sample(logits, rows) if rows else []
+            self.check_kernel_errors()
+        except Exception:
+            out += sched.fail_step(plan)
+            self.last_step_error = True
+            for o in out:
+                if o.finished:
+                    self._params.pop(o.uid, None)
+                    self._seeds.pop(o.uid, None)
+            raise
+        out += sched.commit_step(plan, sampled)
+        for o in out:
+            if o.finished:
+                self._params.pop(o.uid, None)
+                self._seeds.pop(o.uid, None)
+        return out
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling_params=None) -> List[GenerationResult]:
+        """Generate for every prompt (host token ids in, host token ids out)."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        uids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        results = {uid: GenerationResult([], "") for uid in uids}
+        while not self.is_idle():
+            for o in self.schedule_step():
+                if o.uid not in results:
+                    continue
+                if o.token >= 0:
+                    results[o.uid].tokens.append(o.token)
+                if o.finished:
+                    results[o.uid].finish_reason = o.reason.name.lower()
+        return [results[uid] for uid in uids]

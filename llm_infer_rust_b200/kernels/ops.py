@@ -1,0 +1,304 @@
+"""The engine's operations: thin checked wrappers over the package's CUDA kernels.
+
+Every function takes CUDA tensors and launches on the current stream.  There
+is no CPU path and no silent fallback: a CPU tensor, an unsupported dtype or a
+refused size raises.  Matrix products of the bfloat16 engine go to cuBLAS
+through ``torch.mm`` (the reference uses the same library for them:
+src/layers/linear.rs:5-7); everything else is this package's own code.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_cuda_library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+ERROR_BITS = {1: "a token id outside the embedding table", 2: "a cache slot outside the pool",
+              4: "a position beyond the rotary table", 8: "sampling found no valid token"}
+_RC = {-1: "unsupported dtype", -2: "a size the kernel refuses", -3: "misaligned pointer"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported (float32 and bfloat16 are)") from None
+
+
+def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _contig(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_contiguous():
+            raise KernelError("a kernel was given a non-contiguous tensor")
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ok(rc: int, name: str) -> None:
+    if rc == 0:
+        return
+    if rc in _RC:
+        raise KernelError(f"{name}: {_RC[rc]}")
+    raise KernelError(f"{name}: CUDA error {rc} at launch")
+
+
+# --------------------------------------------------------------------------- error word
+_error_words = {}
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    """The device word into which kernels OR their error bits."""
+    key = torch.device(device).index or 0
+    if key not in _error_words:
+        _error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_words[key]
+
+
+def check_errors(device: torch.device) -> None:
+    """Read the error word (synchronises) and raise if a kernel flagged a fault."""
+    word = error_word(device)
+    value = int(word.item())
+    if value:
+        word.zero_()
+        what = [text for bit, text in ERROR_BITS.items() if value & bit]
+        raise KernelError("a kernel refused an access: " + "; ".join(what))
+
+
+# --------------------------------------------------------------------------- libraries
+def _elementwise():
+    return load_cuda_library("elementwise.cu")
+
+
+def _attention(head_dim: int):
+    if head_dim % 16 != 0 or not 16 <= head_dim <= 512:
+        raise KernelError(f"head size {head_dim} is refused: the attention kernels take multiples of 16 "
+                          f"from 16 to 512")
+    return load_cuda_library("attention.cu", {"HEAD_DIM": head_dim})
+
+
+# --------------------------------------------------------------------------- element-wise
+def embedding(ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    _cuda(ids, table)
+    _contig(ids, table)
+    if ids.dtype != torch.int32:
+        raise KernelError("token ids must be int32")
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=out_dtype, device=table.device)
+    rc = _elementwise().b200_embedding(_p(out), _p(table), _p(ids), ids.numel(), table.shape[1],
+                                       table.shape[0], _code(out), _code(table),
+                                       _p(error_word(table.device)), _stream())
+    _ok(rc, "embedding")
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+             rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = rms_norm(x[rows[r]]) * weight (rows None: every row, in place allowed)."""
+    return _norm(x, None, weight, eps, out, rows, False)
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                 out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                 write_residual: bool = True) -> torch.Tensor:
+    """s = x + residual in float; residual <- round(s); out = rms_norm(s) * weight."""
+    return _norm(x, residual, weight, eps, out, rows, write_residual)
+
+
+def _norm(x, residual, weight, eps, out, rows, write_residual):
+    _cuda(x, residual, weight, out, rows)
+    _contig(x, residual, weight, out, rows)
+    width = x.shape[-1]
+    if weight.numel() != width:
+        raise KernelError(f"norm weight has {weight.numel()} elements, the rows have {width}")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype):
+        raise KernelError("the residual must have the shape and dtype of x")
+    n = x.numel() // width if rows is None else rows.numel()
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("row indices must be int32")
+    if out is None:
+        out = torch.empty((n, width), dtype=x.dtype, device=x.device)
+    elif out.dtype != x.dtype or out.numel() != n * width:
+        raise KernelError("norm output has the wrong dtype or size")
+    rc = _elementwise().b200_rms_norm(_p(out), _p(x), _p(residual), _p(weight), _p(rows), n, width,
+                                      ctypes.c_float(eps), int(bool(write_residual)), _code(x),
+                                      _code(weight), _stream())
+    _ok(rc, "rms_norm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _cuda(gate_up, out)
+    _contig(gate_up, out)
+    tokens, width2 = gate_up.shape
+    if width2 % 2:
+        raise KernelError("silu_mul needs an even width")
+    if out is None:
+        out = torch.empty((tokens, width2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    rc = _elementwise().b200_silu_mul(_p(out), _p(gate_up), tokens, width2 // 2, _code(gate_up), _stream())
+    _ok(rc, "silu_mul")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _cuda(x)
+    _contig(x)
+    if x.dtype == dtype:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    rc = _elementwise().b200_cast(_p(out), _p(x), ctypes.c_longlong(x.numel()), _code(out), _code(x), _stream())
+    _ok(rc, "cast")
+    return out
+
+
+# --------------------------------------------------------------------------- between QKV and attention
+def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+             v_cache: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
+             k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+             sin: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
+             slots: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Per-head norm, rotary encoding, cache store.  ``slots`` None: nothing is stored."""
+    _cuda(qkv, q_out, k_cache, v_cache, q_weight, k_weight, cos, sin, positions, slots)
+    _contig(qkv, q_out, k_cache, v_cache, q_weight, k_weight, cos, sin, positions, slots)
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError("qkv width does not match the head counts")
+    if slots is not None and (k_cache is None or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype):
+        raise KernelError("the cache must have the activations' dtype")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("q and k norm weights come together")
+    if cos is not None and (cos.dtype != torch.float32 or sin.dtype != torch.float32):
+        raise KernelError("rotary tables must be float32")
+    wcode = _code(q_weight) if q_weight is not None else _code(qkv)
+    if q_weight is not None and k_weight.dtype != q_weight.dtype:
+        raise KernelError("q and k norm weights must share a dtype")
+    cache_slots = 0 if k_cache is None else k_cache.shape[0] * k_cache.shape[1]
+    max_pos = 0 if cos is None else cos.shape[0]
+    lib = load_cuda_library("qkv_post.cu")
+    rc = lib.b200_qkv_post(_p(qkv), _p(q_out), _p(k_cache), _p(v_cache), _p(q_weight), _p(k_weight),
+                           ctypes.c_float(eps), _p(cos), _p(sin), rot_dim, max_pos, _p(positions), _p(slots),
+                           tokens, num_heads, num_kv_heads, head_dim, ctypes.c_longlong(cache_slots),
+                           _code(qkv), wcode, _p(error_word(qkv.device)), _stream())
+    _ok(rc, "qkv_post")
+
+
+# --------------------------------------------------------------------------- attention
+def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, n_rows,
+                      max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale) -> None:
+    """Causal attention of prompt portions over the paged cache (rows: which batch rows)."""
+    _cuda(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows)
+    _contig(q, k_cache, v_cache, out, block_table)
+    if n_rows == 0:
+        return
+    if k_cache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("q, cache and output must share a dtype")
+    rc = _attention(head_dim).b200_prefill_attention(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
+        _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,
+        int(window or 0), ctypes.c_float(scale), _code(q), _stream())
+    _ok(rc, "prefill_attention")
+
+
+def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: int) -> int:
+    return 0 if splits <= 1 else n_rows * num_heads * splits * (head_dim + 2)
+
+
+def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, n_rows,
+                     num_heads, num_kv_heads, head_dim, page_size, window, scale, splits) -> None:
+    """Attention of single decoded tokens, the keys split over ``splits`` blocks per row."""
+    _cuda(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows)
+    _contig(q, k_cache, v_cache, out, block_table, scratch)
+    if n_rows == 0:
+        return
+    if k_cache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("q, cache and output must share a dtype")
+    need = decode_scratch_floats(n_rows, num_heads, head_dim, splits)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
+        raise KernelError(f"decode attention needs {need} floats of scratch")
+    rc = _attention(head_dim).b200_decode_attention(
+        _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
+        _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
+        ctypes.c_float(scale), splits, _code(q), _stream())
+    _ok(rc, "decode_attention")
+
+
+# --------------------------------------------------------------------------- matrix products
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a[M, K] . w[N, K]^T in true 32-bit on CUDA cores."""
+    _cuda(a, w, out)
+    _contig(a, w, out)
+    if a.dtype != torch.float32 or w.dtype != torch.float32 or a.shape[1] != w.shape[1]:
+        raise KernelError("gemm_f32 takes float32 [M, K] and [N, K]")
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    rc = load_cuda_library("gemm_f32.cu").b200_gemm_f32(_p(a), _p(w), _p(out), m, n, k, _stream())
+    _ok(rc, "gemm_f32")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x[M, K] . weight[N, K]^T, no bias.
+
+    float32 x float32: this package's 32-bit kernel.  bfloat16 x bfloat16: cuBLAS
+    with float accumulation.  A weight that the checkpoint keeps in float32 under a
+    bfloat16 engine is multiplied in 32-bit (the activations are widened first).
+    """
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32 and weight.dtype == torch.float32:
+        return cast(gemm_f32(x, weight), out_dtype)
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        _cuda(x, weight)
+        if out_dtype == torch.bfloat16:
+            return torch.mm(x, weight.t())
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if weight.dtype == torch.float32:
+        return cast(gemm_f32(cast(x, torch.float32), weight), out_dtype)
+    return cast(gemm_f32(x, cast(weight, torch.float32)), out_dtype)
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("argmax takes float32 logits [rows, vocab] with unit inner stride")
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    rc = load_cuda_library("sampling.cu").b200_argmax(_p(logits), ctypes.c_longlong(logits.stride(0)),
+                                                      logits.shape[0], logits.shape[1], _p(out),
+                                                      _p(error_word(logits.device)), _stream())
+    _ok(rc, "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, uniforms: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``params``: uint8 [rows, 32] device tensor of packed rows (see sampling.pack_rows)."""
+    _cuda(logits, params, uniforms)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample takes float32 logits [rows, vocab] with unit inner stride")
+    if params.numel() * params.element_size() != logits.shape[0] * 32:
+        raise KernelError("sampling parameters must hold 32 bytes per row")
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    rc = load_cuda_library("sampling.cu").b200_sample(_p(logits), ctypes.c_longlong(logits.stride(0)),
+                                                      logits.shape[0], logits.shape[1], _p(params), _p(out),
+                                                      _p(uniforms), _p(error_word(logits.device)), _stream())
+    _ok(rc, "sample")
+    return out

@@ -1,0 +1,99 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from .base import PagedKVSpec, ParamDecl, Part
+from .registry import register_part
+
+# Resident CTAs that the split-KV decode kernel aims for per SM.
+_DECODE_CTAS_PER_SM = 2
+_DECODE_KEYS_PER_CTA = 128      # 4 warps x one block of 32 keys
+
+
+def decode_splits(n_rows: int, num_kv_heads: int, group: int, kv_len_bound: int, sm_count: int) -> int:
+    """How many CTAs share one row's keys: enough to fill the GPU, never more than there are key blocks."""
+    per_split_ctas = max(1, n_rows * num_kv_heads * ((group + 3) // 4))
+    want = -(-sm_count * _DECODE_CTAS_PER_SM // per_split_ctas)
+    most = max(1, -(-kv_len_bound // _DECODE_KEYS_PER_CTA))
+    return max(1, min(want, most, 64))
+
+
+class GQAttention(Part):
+    """q, k, v = x W_qkv^T; per-head RMSNorm of q and k; rotary encoding; keys and
+    values go to the cache; causal (optionally windowed) attention over the cache;
+    output projection.  No bias.
+
+    Order and formulas: src/models/qwen3/model.rs:462-534 of the reference; one
+    packed QKV matrix with q rows, then k rows, then v rows (src/layers/linear.rs:25-78).
+    Parameters of the part: head counts, head size, the norm's eps (None: no QK
+    norm), the window (None: all keys), the softmax scale and the name of the
+    model's position encoding.
+    """
+    category = "mixer"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["num_heads"])
+        self.nkv = int(spec["num_kv_heads"])
+        self.d = int(spec["head_dim"])
+        self.qk_eps = spec.get("qk_norm_eps")
+        self.window = spec.get("window")
+        self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d)))
+        if self.nh % self.nkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.d % 16 or not 16 <= self.d <= 512:
+            raise ValueError(f"head_dim {self.d} is refused: the attention kernels take multiples of 16 "
+                             f"from 16 to 512")
+        if self.nh // self.nkv > 32:
+            raise ValueError("more than 32 query heads per KV head are refused by the attention kernels")
+        name = spec.get("position_encoding")
+        self.rope = env.position_encodings[name] if name else None
+
+    def param_decls(self):
+        decls = {"qkv_proj": ParamDecl(((self.nh + 2 * self.nkv) * self.d, self.hidden)),
+                 "o_proj": ParamDecl((self.hidden, self.nh * self.d))}
+        if self.qk_eps is not None:
+            decls["q_norm"] = ParamDecl((self.d,), "vector")
+            decls["k_norm"] = ParamDecl((self.d,), "vector")
+        return decls
+
+    def cache_spec(self):
+        return PagedKVSpec(self.nkv, self.d, self.window)
+
+    def state_spec(self):
+        return None
+
+    def forward(self, x, ctx, cache):
+        p = self.params
+        tokens = x.shape[0]
+        qkv = ops.linear(x, p["qkv_proj"])
+        q = torch.empty((tokens, self.nh * self.d), dtype=x.dtype, device=x.device)
+        rope = self.rope
+        ops.qkv_post(qkv, q, cache.k, cache.v, p.get("q_norm"), p.get("k_norm"),
+                     float(self.qk_eps or 0.0), rope.cos if rope else None, rope.sin if rope else None,
+                     rope.rot_dim if rope else 0, ctx.positions,
+                     ctx.slots[cache.group] if cache.writes else None, self.nh, self.nkv, self.d)
+        out = torch.empty_like(q)
+        g = cache.group
+        page = ctx.page_sizes[g]
+        if ctx.num_prefill:
+            ops.prefill_attention(q, cache.k, cache.v, out, ctx.block_tables[g], ctx.cu_q, ctx.kv_len,
+                                  ctx.prefix_len, ctx.prefill_rows, ctx.num_prefill, ctx.max_q_len,
+                                  self.nh, self.nkv, self.d, page, self.window, self.scale)
+        if ctx.num_decode:
+            bound = min(ctx.kv_len_bound, self.window) if self.window else ctx.kv_len_bound
+            splits = decode_splits(ctx.num_decode, self.nkv, self.nh // self.nkv, bound, ctx.sm_count)
+            need = ops.decode_scratch_floats(ctx.num_decode, self.nh, self.d, splits)
+            scratch = ctx.scratch(need) if need else None
+            ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
+                                 ctx.kv_len, ctx.decode_rows, ctx.num_decode, self.nh, self.nkv, self.d,
+                                 page, self.window, self.scale, splits)
+        return ops.linear(out, p["o_proj"])
+
+
+register_part("mixer", "gqa_attention", GQAttention)

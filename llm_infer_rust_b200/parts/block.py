@@ -1,0 +1,41 @@
+"""Arrangements of a layer's parts."""
+from __future__ import annotations
+
+from .registry import build_part, register_part
+from ..config.spec import PartSpec
+
+
+class PreNormDeferredAdd:
+    """Pre-norm residual block whose adds are folded into the following norm.
+
+    x = norm_in(h + residual); a = mixer(x); x = norm_post(a + residual);
+    h = feed_forward(x).  The feed-forward's output is NOT added here: the next
+    block's input norm (or the model's final norm) adds it.  The first block gets
+    ``residual is None``: then residual = h and x = norm_in(h).
+    Reference: src/models/qwen3/model.rs:424-460, :516-534 and :181-208.
+    """
+    category = "block"
+
+    def __init__(self, layer_spec, env):
+        self.spec = layer_spec
+        self.input_norm = build_part("norm", layer_spec.norm, env)
+        self.post_mixer_norm = build_part("norm", layer_spec.norm, env)
+        self.mixer = build_part("mixer", layer_spec.mixer, env)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, env)
+
+    def children(self):
+        return {"input_norm": self.input_norm, "mixer": self.mixer,
+                "post_mixer_norm": self.post_mixer_norm, "feed_forward": self.feed_forward}
+
+    def forward(self, h, residual, ctx, cache):
+        if residual is None:
+            residual = h
+            x = self.input_norm.forward(h)
+        else:
+            x = self.input_norm.forward_add(h, residual, out=h)
+        a = self.mixer.forward(x, ctx, cache)
+        x = self.post_mixer_norm.forward_add(a, residual, out=a)
+        return self.feed_forward.forward(x), residual
+
+
+register_part("block", "pre_norm_deferred_add", PreNormDeferredAdd)

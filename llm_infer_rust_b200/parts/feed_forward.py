@@ -1,0 +1,31 @@
+"""Feed-forward parts."""
+from __future__ import annotations
+
+from ..kernels import ops
+from .base import ParamDecl, Part
+from .registry import register_part
+
+
+class SwiGLU(Part):
+    """down(silu(gate(x)) * up(x)) with gate and up packed into one matrix, no bias.
+
+    ``gate_up_proj`` is [2 I, H] with the gate rows first (reference:
+    src/layers/mlp.rs:7-25, packing src/models/qwen3/model.rs:577-586).
+    """
+    category = "feed_forward"
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+
+    def param_decls(self):
+        return {"gate_up_proj": ParamDecl((2 * self.inter, self.hidden)),
+                "down_proj": ParamDecl((self.hidden, self.inter))}
+
+    def forward(self, x):
+        gate_up = ops.linear(x, self.params["gate_up_proj"])
+        return ops.linear(ops.silu_mul(gate_up), self.params["down_proj"])
+
+
+register_part("feed_forward", "swiglu", SwiGLU)
