@@ -1,3 +1,3 @@
-from .paged import CachePlan, GroupPlan, PagedCache, cache_budget_bytes, plan_cache, size_groups
+from .paged import CachePlan, GroupPlan, LayerCache, PagedCache, cache_budget_bytes, plan_cache, size_groups
 
-__all__ = ["CachePlan", "GroupPlan", "PagedCache", "cache_budget_bytes", "plan_cache", "size_groups"]
+__all__ = ["CachePlan", "GroupPlan", "LayerCache", "PagedCache", "cache_budget_bytes", "plan_cache", "size_groups"]

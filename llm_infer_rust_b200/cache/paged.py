@@ -25,8 +25,17 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..engine.context import LayerCache
 from ..kernels.build import load_host_runtime
+
+
+@dataclass
+class LayerCache:
+    """The cache of one entry of the run list."""
+    group: int = -1                          # cache group of the pages, -1: no paged cache
+    k: Optional[torch.Tensor] = None         # [pages + 1, page_size, kv_heads, head_dim]
+    v: Optional[torch.Tensor] = None
+    writes: bool = True                      # False: this entry reads another entry's pages
+    state: Optional[torch.Tensor] = None     # [slots + 1, *state_shape]; slot 0 is the sink
 
 
 @dataclass

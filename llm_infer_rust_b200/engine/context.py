@@ -49,11 +49,30 @@ class StepContext:
     extras: dict = field(default_factory=dict)
 
 
-@dataclass
-class LayerCache:
-    """The cache of one entry of the run list."""
-    group: int = -1                          # cache group of the pages, -1: no paged cache
-    k: Optional[torch.Tensor] = None         # [pages + 1, page_size, kv_heads, head_dim]
-    v: Optional[torch.Tensor] = None
-    writes: bool = True                      # False: this entry reads another entry's pages
-    state: Optional[torch.Tensor] = None     # [slots + 1, *state_shape]; slot 0 is the sink
+def context_from_layout(layout, dev: torch.Tensor, host: Optional[torch.Tensor], page_sizes: List[int],
+                        device: torch.device, dtype: torch.dtype, kv_len_bound: int,
+                        scratch: Optional[Callable[[int], torch.Tensor]] = None,
+                        sm_count: int = 148) -> StepContext:
+    """Views of the device buffer ``dev`` that the batch builder's ``layout`` describes."""
+    def view(off, n):
+        return dev[off:off + n]
+
+    groups = len(page_sizes)
+    T, R = layout.num_tokens, layout.num_rows
+    return StepContext(
+        device=device, dtype=dtype, num_tokens=T, num_rows=R, num_decode=layout.num_decode,
+        num_prefill=layout.num_prefill, num_logits=layout.num_logits, max_q_len=layout.max_q_len,
+        max_kv_len=layout.max_kv_len,
+        token_ids=view(layout.off_tokens, T), positions=view(layout.off_positions, T),
+        row_of_token=view(layout.off_row_of_token, T), cu_q=view(layout.off_cu_q, R + 1),
+        kv_len=view(layout.off_kv_len, R), prefix_len=view(layout.off_prefix_len, R),
+        state_slots=view(layout.off_state_slot, R),
+        decode_rows=view(layout.off_decode_rows, layout.num_decode),
+        prefill_rows=view(layout.off_prefill_rows, layout.num_prefill),
+        logit_rows=view(layout.off_logit_rows, layout.num_logits),
+        slots=[view(layout.off_slots[g], T) for g in range(groups)],
+        block_tables=[view(layout.off_table[g], R * layout.table_width[g]).view(R, layout.table_width[g])
+                      for g in range(groups)],
+        page_sizes=list(page_sizes),
+        host=None if host is None else host.numpy(), layout=layout, kv_len_bound=kv_len_bound,
+        scratch=scratch, sm_count=sm_count)

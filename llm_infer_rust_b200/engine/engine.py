@@ -29,7 +29,7 @@ from ..kernels.build import load_host_runtime
 from ..parts import DecoderModel
 from ..sampling import Sampler, SamplingParams
 from ..weights.loader import load_weights, read_config_json
-from .context import StepContext
+from .context import StepContext, context_from_layout
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -241,28 +241,8 @@ class Engine:
         return self._scratch
 
     def _context(self, layout, dev: torch.Tensor, host: Optional[torch.Tensor], kv_len_bound: int) -> StepContext:
-        def view(off, n):
-            return dev[off:off + n]
-
-        groups = len(self.cache.page_sizes)
-        T, R = layout.num_tokens, layout.num_rows
-        return StepContext(
-            device=self.device, dtype=self.dtype, num_tokens=T, num_rows=R, num_decode=layout.num_decode,
-            num_prefill=layout.num_prefill, num_logits=layout.num_logits, max_q_len=layout.max_q_len,
-            max_kv_len=layout.max_kv_len,
-            token_ids=view(layout.off_tokens, T), positions=view(layout.off_positions, T),
-            row_of_token=view(layout.off_row_of_token, T), cu_q=view(layout.off_cu_q, R + 1),
-            kv_len=view(layout.off_kv_len, R), prefix_len=view(layout.off_prefix_len, R),
-            state_slots=view(layout.off_state_slot, R),
-            decode_rows=view(layout.off_decode_rows, layout.num_decode),
-            prefill_rows=view(layout.off_prefill_rows, layout.num_prefill),
-            logit_rows=view(layout.off_logit_rows, layout.num_logits),
-            slots=[view(layout.off_slots[g], T) for g in range(groups)],
-            block_tables=[view(layout.off_table[g], R * layout.table_width[g]).view(R, layout.table_width[g])
-                          for g in range(groups)],
-            page_sizes=list(self.cache.page_sizes),
-            host=None if host is None else host.numpy(), layout=layout, kv_len_bound=kv_len_bound,
-            scratch=self._get_scratch, sm_count=self.sm_count)
+        return context_from_layout(layout, dev, host, self.cache.page_sizes, self.device, self.dtype,
+                                   kv_len_bound, self._get_scratch, self.sm_count)
 
     def _batch_request(self, entries: Sequence[StepEntry]):
         req = self._rt.BatchRequest()
