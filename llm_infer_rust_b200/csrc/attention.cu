@@ -241,9 +241,8 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
 // (vector group vg holds heads kvh * group + 4 * vg ..).  Split s of a row covers an equal share of
 // the row's key blocks; it writes (max, sum, unnormalised output) per head to scratch, or the
 // final output when there is one split.
-constexpr int DEC_WARPS = 4;
-
-template <typename T>
+// DEC_WARPS is 4 where the tiles of four warps fit shared memory, else 2 or 1 (large heads in float).
+template <typename T, int DEC_WARPS>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                         T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
@@ -420,23 +419,26 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int vec_groups = (group + NV - 1) / NV;
-  const size_t tile_bytes = 2 * KB * G::STRIDE * sizeof(T);
-  const size_t fixed = (NV * D + DEC_WARPS * KB * NV) * sizeof(float);
-  int stages = 2;
-  if (fixed + DEC_WARPS * 2 * tile_bytes > 200 * 1024) stages = 1;
+  constexpr size_t tile_bytes = 2 * KB * G::STRIDE * sizeof(T);
+  constexpr size_t limit = 200 * 1024;
+  constexpr size_t fixed4 = (NV * D + 4 * KB * NV) * sizeof(float);
+  // Four warps with two stages where that fits, else one stage, else fewer warps.
+  constexpr int DEC_WARPS = fixed4 + 4 * tile_bytes <= limit ? 4 : (fixed4 + 2 * tile_bytes <= limit ? 2 : 1);
+  constexpr size_t fixed = (NV * D + DEC_WARPS * KB * NV) * sizeof(float);
+  static_assert(fixed + DEC_WARPS * tile_bytes <= 220 * 1024, "one key block per warp must fit shared memory");
+  const int stages = fixed + DEC_WARPS * 2 * tile_bytes <= limit ? 2 : 1;
   size_t smem = fixed + DEC_WARPS * stages * tile_bytes;
   const size_t merge_bytes = DEC_WARPS * NV * (D + 2) * sizeof(float);
   if (fixed + merge_bytes > smem) smem = fixed + merge_bytes;
-  if (smem > 220 * 1024) return B200_BAD_SIZE;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<T, DEC_WARPS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = smem;
   }
   dim3 grid(splits, nkv * vec_groups, n_rows);
-  decode_attention_kernel<T><<<grid, DEC_WARPS * 32, smem, stream>>>(
+  decode_attention_kernel<T, DEC_WARPS><<<grid, DEC_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size, window, scale,
       vec_groups, stages);

@@ -29,6 +29,7 @@ from ..kernels.build import load_host_runtime
 from ..parts import DecoderModel
 from ..sampling import Sampler, SamplingParams
 from ..weights.loader import load_weights, read_config_json
+from ..weights.random_init import bind_random_weights
 from .context import StepContext, context_from_layout
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -80,6 +81,7 @@ class _MetaBuffers:
         self.events: List[Optional[torch.cuda.Event]] = []
         self.dev: Optional[torch.Tensor] = None
         self.turn = 0
+        self.last_bytes = 0
 
     def reserve(self, ints: int) -> None:
         if ints <= self.capacity:
@@ -99,6 +101,7 @@ class _MetaBuffers:
 
     def upload(self, turn: int, ints: int, dst: Optional[torch.Tensor] = None) -> torch.Tensor:
         dst = self.dev if dst is None else dst
+        self.last_bytes = 4 * ints
         dst[:ints].copy_(self.pinned[turn][:ints], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -114,18 +117,25 @@ class _DecodeGraph:
         self.ctx: Optional[StepContext] = None
         self.logits: Optional[torch.Tensor] = None
         self.layout_key = None
+        self.launches = 0          # kernels of this package inside the graph
 
 
 class Engine:
-    def __init__(self, model_path: str, *, dtype: str = "auto", device: str = "cuda",
+    def __init__(self, model_path: Optional[str], *, dtype: str = "auto", device: str = "cuda",
                  max_running_req: int = 256, max_seq_len: Optional[int] = None, page_size: int = 16,
                  memory_ratio: float = 0.9, max_total_tokens: Optional[int] = None,
                  max_prefill_tokens_per_batch: int = 8192, chunked_prefill_size: Optional[int] = None,
                  cuda_graph_bs: Optional[int] = 0, eos_token_ids: Optional[Sequence[int]] = None,
-                 seed: int = 0, log_level: str = "info"):
+                 seed: int = 0, log_level: str = "info", random_weights_config: Optional[dict] = None,
+                 random_weights_seed: int = 0):
+        """``model_path``: a folder with config.json and model.safetensors.  With ``model_path`` None and
+        ``random_weights_config`` (the keys of a config.json) the weights are drawn on the device from
+        ``random_weights_seed`` and no file is read: for sizes whose checkpoint would take long to write."""
         self.model_path = model_path
         self.log_level = log_level
-        raw = read_config_json(model_path)
+        if model_path is None and random_weights_config is None:
+            raise ConfigError("a model folder (or random_weights_config) is needed")
+        raw = dict(random_weights_config) if model_path is None else read_config_json(model_path)
         self.arch = resolve_architecture(raw)
         self.config = self.arch.parse_config(raw)
         self.raw_config = raw
@@ -162,8 +172,12 @@ class Engine:
         torch.backends.cudnn.allow_tf32 = False
 
         self.model = DecoderModel(spec, self.dtype, self.device)
-        self.loaded_tensors = load_weights(self.model, self.arch.weight_plan(self.config), model_path,
-                                           self.dtype, self.device)
+        if model_path is None:
+            self.loaded_tensors = bind_random_weights(self.model, self.arch.weight_plan(self.config),
+                                                      random_weights_seed, self.dtype, self.device)
+        else:
+            self.loaded_tensors = load_weights(self.model, self.arch.weight_plan(self.config), model_path,
+                                               self.dtype, self.device)
         unbound = self.model.unbound_parameters()
         if unbound:
             raise RuntimeError(f"the weight plan of {self.arch.name} left parameters unbound: {unbound}")
@@ -190,7 +204,6 @@ class Engine:
         self._scratch: Optional[torch.Tensor] = None
         self._params: Dict[int, SamplingParams] = {}
         self._seeds: Dict[int, int] = {}
-        self.kernel_launches = 0
 
         self._graphs: Dict[int, _DecodeGraph] = {}
         if cuda_graph_bs is None:
@@ -253,10 +266,13 @@ class Engine:
         req.want_index = [int(i) for e in entries for i in e.want]
         return req
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; float32 logits [wanted, vocab] in the order of the entries and their ``want``.
 
         The tensor may be overwritten by the next step; copy it if it must outlive that.
+        ``device_tokens`` (int32, one per entry, on the device) replaces the entries' token ids when every
+        entry brings exactly one token: a token sampled by the step before can go straight into this one
+        without a trip to the host.
         """
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -274,29 +290,35 @@ class Engine:
                                   f"{[mgr.free_pages(g) for g in range(mgr.num_groups())]}")
         req = self._batch_request(entries)
         decode_only = all(c == 1 for c in req.counts)
+        if device_tokens is not None and (not decode_only or device_tokens.numel() != len(entries)
+                                          or device_tokens.dtype != torch.int32 or not device_tokens.is_cuda):
+            raise ValueError("device_tokens needs one int32 token on the device for each one-token entry")
         graph = None
         if decode_only and self._graphs and all(len(e.want) == 1 for e in entries):
             bucket = next((b for b in sorted(self._graphs) if b >= len(entries)), None)
             if bucket is not None and max(mgr.length(e.request) for e in entries) < self.max_seq_len:
                 graph = self._graphs[bucket]
         if graph is not None:
-            logits = self._step_graph(graph, req, len(entries))
+            logits = self._step_graph(graph, req, len(entries), device_tokens)
         else:
-            logits = self._step_eager(req)
+            logits = self._step_eager(req, device_tokens)
         for e in entries:
             mgr.advance(e.request, mgr.length(e.request) + len(e.tokens))
         return logits
 
-    def _step_eager(self, req) -> torch.Tensor:
+    def _step_eager(self, req, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         layout = self._rt.plan_batch(self.cache.manager, req)
         self._meta.reserve(layout.total_ints)
         turn, host = self._meta.next_host()
         layout = self._rt.build_batch(self.cache.manager, req, host.numpy())
         dev = self._meta.upload(turn, layout.total_ints)
+        if device_tokens is not None:
+            dev[layout.off_tokens:layout.off_tokens + layout.num_tokens].copy_(device_tokens, non_blocking=True)
         ctx = self._context(layout, dev, host, layout.max_kv_len)
         return self.model.forward(ctx, self.cache.layer_caches)
 
-    def _step_graph(self, g: _DecodeGraph, req, real_rows: int) -> torch.Tensor:
+    def _step_graph(self, g: _DecodeGraph, req, real_rows: int,
+                    device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         req.pad_rows_to = g.bucket
         req.fixed_table_width = list(self.table_width)
         layout = self._rt.plan_batch(self.cache.manager, req)
@@ -315,13 +337,19 @@ class Engine:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize(self.device)
             g.graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
             with torch.cuda.graph(g.graph):
                 g.logits = self.model.forward(g.ctx, self.cache.layer_caches)
+            g.launches = ops.launch_count() - before
+            ops.add_launches(-g.launches)        # captured, not run
             g.layout_key = layout.total_ints
         elif layout.total_ints != g.layout_key:
             raise RuntimeError("a decode graph was given a batch of another shape than it was captured for")
         self._meta.upload(turn, layout.total_ints, g.meta)
+        if device_tokens is not None:
+            g.meta[layout.off_tokens:layout.off_tokens + real_rows].copy_(device_tokens, non_blocking=True)
         g.graph.replay()
+        ops.add_launches(g.launches)
         return g.logits[:real_rows]
 
     def capture_graphs(self) -> None:
@@ -342,6 +370,11 @@ class Engine:
             finally:
                 for rid in ids:
                     self.close_request(rid)
+
+    @property
+    def last_upload_bytes(self) -> int:
+        """Bytes of index arrays that the last step copied from pinned host memory to the device."""
+        return self._meta.last_bytes
 
     def check_kernel_errors(self) -> None:
         ops.check_errors(self.device)

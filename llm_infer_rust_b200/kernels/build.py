@@ -161,6 +161,12 @@ def load_cuda_library(source: str, defines: Optional[Dict[str, object]] = None) 
         return lib
 
 
+def all_cuda_libraries(head_dims: Iterable[int]) -> List[tuple]:
+    """(source, defines) of every CUDA library that the package can ask for, attention for ``head_dims``."""
+    libs = [(f, None) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu") and f != "attention.cu"]
+    return libs + [("attention.cu", {"HEAD_DIM": int(d)}) for d in head_dims]
+
+
 def _host_sources() -> List[str]:
     d = os.path.join(CSRC, "host")
     return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith((".cpp", ".h")))

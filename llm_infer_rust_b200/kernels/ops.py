@@ -53,8 +53,22 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _ok(rc: int, name: str) -> None:
+# Launches of this package's kernels so far (library matrix products are not counted).
+_launches = [0]
+
+
+def launch_count() -> int:
+    return _launches[0]
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels that ran without passing through a wrapper (a replayed graph)."""
+    _launches[0] += n
+
+
+def _ok(rc: int, name: str, kernels: int = 1) -> None:
     if rc == 0:
+        _launches[0] += kernels
         return
     if rc in _RC:
         raise KernelError(f"{name}: {_RC[rc]}")
@@ -237,7 +251,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
         _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
         ctypes.c_float(scale), splits, _code(q), _stream())
-    _ok(rc, "decode_attention")
+    _ok(rc, "decode_attention", 2 if splits > 1 else 1)
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -70,3 +70,35 @@ def write_random_model(model_dir: str, raw_config: dict, seed: int, std: float =
         json.dump(config, fh, indent=1)
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors.items())
     return model_dir
+
+
+def bind_random_weights(model, plan, seed: int, engine_dtype: torch.dtype, device: torch.device,
+                        std: float = 0.02, norm_std: float = 0.0):
+    """Fill ``model`` with random weights drawn on ``device``; nothing is written or read.
+
+    Same distributions as ``random_tensors`` (the values differ: the device's generator draws them).
+    Returns the checkpoint names that a folder of this model would hold.
+    """
+    names = []
+    deferred = []
+    for binding in plan:
+        if binding.optional and binding.alias_of is not None:
+            deferred.append(binding)
+            continue
+        parts = []
+        for src in binding.sources:
+            g = torch.Generator(device=device)
+            g.manual_seed((int(seed) * 1_000_003 + zlib.crc32(src.name.encode())) % (2 ** 63 - 1))
+            if src.integer:
+                value = torch.randint(0, 2 ** 15, src.shape, generator=g, dtype=torch.int32, device=device)
+            elif src.init == "norm":
+                value = (1.0 + norm_std * torch.randn(src.shape, generator=g, dtype=torch.float32,
+                                                      device=device)).to(engine_dtype)
+            else:
+                value = torch.randn(src.shape, generator=g, dtype=engine_dtype, device=device).mul_(std)
+            parts.append(value)
+            names.append(src.name)
+        model.bind_parameter(binding.param, parts[0] if len(parts) == 1 else torch.cat(parts, dim=0))
+    for binding in deferred:
+        model.bind_parameter(binding.param, model.parameter(binding.alias_of))
+    return names

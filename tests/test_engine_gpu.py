@@ -1,0 +1,241 @@
+"""The engine through its entry points: ``generate``, the scheduler loop, the command line,
+decode graphs, long decoding, and what happens when pages run out."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def tokens(vocab, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def engine(folder, **kw):
+    from llm_infer_rust_b200.engine import Engine
+    kw.setdefault("cuda_graph_bs", 0)
+    kw.setdefault("max_running_req", 4)
+    return Engine(folder, **kw)
+
+
+def confident_greedy(weights, raw, prompt, n):
+    """Greedy continuation by the plain implementation, and the margin between its two best logits."""
+    seq, out, margin = list(prompt), [], float("inf")
+    for _ in range(n):
+        last = P.plain_forward(weights, raw, seq)[-1]
+        top = torch.topk(last, 2).values
+        margin = min(margin, float(top[0] - top[1]))
+        out.append(int(last.argmax()))
+        seq.append(out[-1])
+    return out, margin
+
+
+def test_greedy_generation_matches_the_plain_implementation(tiny, tiny_weights, tiny_dirs):
+    from llm_infer_rust_b200 import SamplingParams
+    raw = tiny["A"]["raw"]
+    prompts = [tokens(256, n, 20 + n) for n in (5, 9, 17)]
+    eng = engine(tiny_dirs["A"], dtype="float32", page_size=4, max_total_tokens=256)
+    got = eng.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    for prompt, res in zip(prompts, got):
+        want, margin = confident_greedy(tiny_weights["A"], raw, prompt, 8)
+        assert margin > 1e-4, "the test's own prompt leaves a near tie; choose another seed"
+        assert res.tokens == want and res.finish_reason == "length"
+    assert eng.cache.manager.live_requests() == 0 and eng.cache.manager.check() == ""
+    # a stop id ends a request with the id emitted
+    stop = got[0].tokens[3]
+    eng2 = engine(tiny_dirs["A"], dtype="float32", page_size=4, max_total_tokens=256, eos_token_ids=[stop])
+    res = eng2.generate([prompts[0]], SamplingParams(max_tokens=8))[0]
+    first = got[0].tokens.index(stop)
+    assert res.tokens == got[0].tokens[: first + 1] and res.finish_reason == "stop"
+    res = eng2.generate([prompts[0]], SamplingParams(max_tokens=8, ignore_eos=True))[0]
+    assert res.tokens == got[0].tokens
+
+
+# ----------------------------------------------------------------------------- temperature sampling
+def philox_uniform(seed, counter):
+    """Philox4x32-10 with counter (counter, 0, 0x1234567, 0) and key (seed lo, seed hi): the first word / 2^24."""
+    M0, M1, W0, W1, mask = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85, 0xFFFFFFFF
+    c = [counter & mask, 0, 0x1234567, 0]
+    k0, k1 = seed & mask, (seed >> 32) & mask
+    for _ in range(10):
+        p0, p1 = M0 * c[0], M1 * c[2]
+        c = [(p1 >> 32) ^ c[1] ^ k0, p1 & mask, (p0 >> 32) ^ c[3] ^ k1, p0 & mask]
+        k0, k1 = (k0 + W0) & mask, (k1 + W1) & mask
+    return (c[0] >> 8) / 16777216.0
+
+
+def test_temperature_sampling_is_the_inverse_cdf_of_a_keyed_uniform(tiny, tiny_weights, tiny_dirs):
+    """Tiny B: prompts 1/7/33/70, portions of 16, mixed batches, temperature 0.8, a fixed seed, 12 tokens.
+    Every sampled token is where the plain distribution's cumulative sum passes the uniform number
+    that (seed, output index) give; so it cannot depend on the batch."""
+    from llm_infer_rust_b200 import SamplingParams
+    raw, w = tiny["B"]["raw"], tiny_weights["B"]
+    prompts = [tokens(509, n, 40 + n) for n in (1, 7, 33, 70)]
+    sp = [SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=1000 + i) for i in range(4)]
+    eng = engine(tiny_dirs["B"], dtype="float32", page_size=16, max_total_tokens=512, chunked_prefill_size=16)
+    together = eng.generate(prompts, sp)
+    alone = [eng.generate([p], [s])[0] for p, s in zip(prompts, sp)]
+    assert [r.tokens for r in together] == [r.tokens for r in alone]
+    other_seed = eng.generate([prompts[3]], [SamplingParams(temperature=0.8, max_tokens=12, ignore_eos=True, seed=7)])[0]
+    assert other_seed.tokens != together[3].tokens
+    checked = 0
+    for i, (prompt, res) in enumerate(zip(prompts, together)):
+        assert len(res.tokens) == 12
+        logits = P.plain_forward(w, raw, prompt + res.tokens[:-1])[len(prompt) - 1:]
+        cdf = torch.softmax(logits / 0.8, -1).cumsum(-1)
+        for k, tok in enumerate(res.tokens):
+            u = philox_uniform(1000 + i, k) * float(cdf[k, -1])
+            want = int((cdf[k] <= u).sum())
+            gap = float((cdf[k] - u).abs().min())
+            if gap > 1e-5:                                    # away from a boundary the draw is unambiguous
+                assert tok == want, (i, k, tok, want, gap)
+                checked += 1
+    assert checked >= 40
+
+
+def test_when_pages_run_out_requests_wait_and_results_do_not_change(tiny, tiny_dirs):
+    from llm_infer_rust_b200 import SamplingParams
+    prompts = [tokens(301, n, 60 + n) for n in (50, 20, 64, 9, 33, 41, 70, 5)]
+    sp = SamplingParams(max_tokens=20, ignore_eos=True)
+    roomy = engine(tiny_dirs["C"], dtype="float32", page_size=8, max_total_tokens=2048, max_running_req=8,
+                   chunked_prefill_size=32)
+    want = [r.tokens for r in roomy.generate(prompts, sp)]
+    # 24 pages of 8 = 192 tokens: two or three requests fit at a time, the rest wait at the head of the queue
+    tight = engine(tiny_dirs["C"], dtype="float32", page_size=8, max_total_tokens=192, max_running_req=8,
+                   chunked_prefill_size=32)
+    uids = [tight.add_request(p, sp) for p in prompts]
+    out = {u: [] for u in uids}
+    most_running, steps = 0, 0
+    while not tight.is_idle():
+        for o in tight.schedule_step():
+            out[o.uid].append(o.token)
+        most_running = max(most_running, tight.scheduler.num_running())
+        assert tight.cache.manager.check() == ""
+        steps += 1
+        assert steps < 2000
+    assert [out[u] for u in uids] == want
+    assert most_running < 8 and tight.cache.manager.free_pages(0) == 24
+    # a request that can never fit is aborted, the others are served
+    res = tight.generate([tokens(301, 150, 1), prompts[3]], SamplingParams(max_tokens=100, ignore_eos=True))
+    assert res[0].finish_reason == "abort" and res[0].tokens == [] and len(res[1].tokens) == 100
+
+
+def test_long_decoding_stays_on_the_plain_logits(tiny, tiny_weights, tiny_dirs, tmp_path):
+    """Three hundred tokens decoded one by one (windows slide, pages are given back on the way)."""
+    from llm_infer_rust_b200.engine import StepEntry
+    raw, w = tiny["C"]["raw"], tiny_weights["C"]
+    ids = tokens(301, 318, 77)
+    want = P.plain_forward(w, raw, ids).numpy()
+    for dtype, tol in (("float32", 1e-5), ("bfloat16", 2.0 ** -5)):
+        ww = w if dtype == "float32" else {n: t.to(torch.bfloat16) for n, t in w.items()}
+        ref = want if dtype == "float32" else P.plain_forward(ww, raw, ids).numpy()
+        folder = tiny_dirs["C"]
+        if dtype == "bfloat16":                               # a checkpoint stored in bfloat16
+            from llm_infer_rust_b200 import write_random_model
+            v = tiny["C"]
+            folder = write_random_model(str(tmp_path / "bf16"), v["raw"], v["seed"], norm_std=v["norm_std"],
+                                        dtype="bfloat16")
+        eng = engine(folder, dtype=dtype, page_size=8, max_total_tokens=512)
+        eng.open_request(1)
+        rows = [eng.step([StepEntry(1, ids[:18], list(range(18)))]).cpu().numpy()]
+        for t in range(18, 318):
+            rows.append(eng.step([StepEntry(1, [ids[t]], [0])]).cpu().numpy())
+        eng.check_kernel_errors()
+        got = np.concatenate(rows)
+        held = eng.cache.manager.pages_held(1, [g.window for g in eng.cache_plan.groups].index(40))
+        assert held <= 40 // 8 + 2                            # the windowed group kept only its window
+        err = np.abs(got - ref).max(axis=1)
+        assert err.max() <= tol * max(1.0, np.abs(ref).max()), (dtype, int(err.argmax()), err.max())
+
+
+def test_decode_graphs_give_the_eager_logits(tiny, tiny_dirs, tmp_path):
+    from llm_infer_rust_b200 import SamplingParams, write_random_model
+    from llm_infer_rust_b200.engine import StepEntry
+    v = tiny["B"]
+    folder = write_random_model(str(tmp_path / "m"), v["raw"], v["seed"], norm_std=v["norm_std"], dtype="bfloat16")
+    prompts = [tokens(509, n, 80 + n) for n in (3, 40, 17)]
+    eager = engine(folder, dtype="bfloat16", max_total_tokens=512)
+    graph = engine(folder, dtype="bfloat16", max_total_tokens=512, cuda_graph_bs=4)
+    assert sorted(graph._graphs) == [1, 2, 4]
+    for eng in (eager, graph):
+        for r, p in enumerate(prompts):
+            eng.open_request(r + 1)
+            eng.step([StepEntry(r + 1, p, [])])
+    nxt = [5, 6, 7]
+    for step in range(20):
+        live = [r for r in range(3) if not (r == 1 and step >= 10)]        # the batch shrinks: another bucket, padded rows
+        entries = [StepEntry(r + 1, [nxt[r]], [0]) for r in live]
+        a = eager.step(entries).clone()
+        b = graph.step(entries).clone()
+        # the padded batch may take another library matrix kernel: equal up to bfloat16 rounding
+        assert (a - b).abs().max() <= 2.0 ** -6 * max(1.0, float(a.abs().max())), step
+        nxt = [int(x) % 509 for x in (a.argmax(-1).tolist() + [0, 0, 0])[:3]]
+    assert graph._graphs[4].graph is not None and graph._graphs[2].graph is not None
+    graph.check_kernel_errors()
+    sp = SamplingParams(max_tokens=16, ignore_eos=True)
+    for eng in (eager, graph):
+        for r in range(3):
+            eng.close_request(r + 1)
+    res = graph.generate(prompts, sp)
+    assert [len(r.tokens) for r in res] == [16, 16, 16] and graph.cache.manager.live_requests() == 0
+
+
+def test_command_line(tiny, tiny_dirs, tmp_path):
+    from llm_infer_rust_b200 import SamplingParams
+    want = engine(tiny_dirs["A"], dtype="float32", page_size=4, max_total_tokens=256).generate(
+        [[1, 2, 3], [9, 8, 7, 6]], SamplingParams(max_tokens=5, ignore_eos=True))
+    cmd = [sys.executable, "-m", "llm_infer_rust_b200", "--model-path", tiny_dirs["A"], "--dtype", "float32",
+           "--page-size", "4", "--max-total-tokens", "256", "--max-running-req", "4", "--max-seq-len", "64",
+           "--cuda-graph-bs", "0", "--prompt-ids", "1,2,3", "--prompt-ids", "9,8,7,6", "--max-tokens", "5", "--ignore-eos"]
+    done = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    lines = [json.loads(x) for x in done.stdout.strip().splitlines()]
+    assert [x["output_ids"] for x in lines] == [r.tokens for r in want]
+    assert lines[0]["prompt_ids"] == [1, 2, 3] and lines[0]["finish_reason"] == "length"
+    # random-weights mode writes the folder and serves it
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(tiny["A"]["raw"]))
+    out_dir = tmp_path / "made"
+    cmd = [sys.executable, "-m", "llm_infer_rust_b200", "--model-path", str(out_dir), "--random-weights", "--config",
+           str(cfg), "--seed", "0", "--dtype", "float32", "--page-size", "4", "--max-total-tokens", "256",
+           "--max-running-req", "4", "--cuda-graph-bs", "0", "--prompt-ids", "1,2,3", "--max-tokens", "5", "--ignore-eos"]
+    done = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    assert sorted(os.listdir(out_dir)) == ["config.json", "model.safetensors"]
+    assert json.loads(done.stdout.strip())["output_ids"] == want[0].tokens      # seed 0 is the fixture's seed
+    bad = subprocess.run([sys.executable, "-m", "llm_infer_rust_b200", "--model-path", tiny_dirs["A"],
+                          "--max-seq-len", "4096", "--prompt-ids", "1"], cwd=ROOT, capture_output=True, text=True)
+    assert bad.returncode != 0 and "max_position_embeddings" in bad.stderr
+
+
+def test_refusals_at_start_up_and_in_a_step(tiny, tiny_dirs, tmp_path):
+    from llm_infer_rust_b200 import ConfigError
+    from llm_infer_rust_b200.engine import Engine, StepEntry
+    with pytest.raises(ConfigError, match="max_position_embeddings"):
+        Engine(tiny_dirs["A"], max_seq_len=129)
+    with pytest.raises(ConfigError, match="CUDA only"):
+        Engine(tiny_dirs["A"], device="cpu")
+    unsupported = tmp_path / "moe"
+    unsupported.mkdir()
+    (unsupported / "config.json").write_text(json.dumps(dict(tiny["A"]["raw"], model_type="qwen3_moe",
+                                                             architectures=["Qwen3MoeForCausalLM"])))
+    with pytest.raises(ConfigError, match="unsupported model"):       # before any weight is looked for
+        Engine(str(unsupported))
+    eng = engine(tiny_dirs["A"], dtype="float32", page_size=4, max_total_tokens=32)
+    eng.open_request(1)
+    with pytest.raises(MemoryError, match="no pages left"):
+        eng.step([StepEntry(1, list(range(40)), [])])
+    with pytest.raises(ValueError, match="at least one token"):
+        eng.step([StepEntry(1, [], [])])
+    eng.step([StepEntry(1, [1, 2, 300], [])])                          # 300 is outside the vocabulary of 256
+    with pytest.raises(Exception, match="token id"):
+        eng.check_kernel_errors()
