@@ -168,8 +168,9 @@ def decode_end_to_end(engine, batch, context, steps, warmup, vocab):
     """The same through the public scheduler loop: host token ids in, host token ids out, every step."""
     import torch
     from llm_infer_rust_b200 import SamplingParams
-    prompt_len = context - steps - warmup
-    sp = SamplingParams(max_tokens=steps + warmup + 1, ignore_eos=True)
+    # prompts enter one a step, so the first request decodes up to `batch` tokens before the last is in
+    prompt_len = context - steps - warmup - batch
+    sp = SamplingParams(max_tokens=steps + warmup + 2 * batch + 8, ignore_eos=True)
     for r in range(batch):
         engine.add_request(random_prompt(vocab, prompt_len, 2000 + r), sp)
     while engine.scheduler.num_pending() or any(
@@ -224,6 +225,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one phase alone and print a short line (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -244,13 +247,20 @@ def main() -> int:
     vocab = raw["vocab_size"]
     numbers = model_numbers(raw)
     peak, peak_source = peaks()
-    biggest = 1 if args.no_points else max(64, args.batch)
-    biggest = max(biggest, args.batch)
-    pool_tokens = biggest * (args.context + 64) + 4096
+    biggest = args.batch if (args.no_points or args.only) else max(64, args.batch)
+    pool_tokens = biggest * (args.context + 128) + 4096
     engine = Engine(None, random_weights_config=raw, random_weights_seed=0, dtype="bfloat16",
-                    max_running_req=biggest, max_seq_len=args.context + 16, page_size=16,
+                    max_running_req=biggest, max_seq_len=args.context + 64, page_size=16,
                     max_total_tokens=pool_tokens, cuda_graph_bs=biggest, chunked_prefill_size=4096)
 
+    if args.only == "decode":
+        run = decode_device_timed(engine, args.batch, args.context, args.steps, args.warmup, vocab)
+        print(json.dumps({"only": "decode", "batch": args.batch, **{k: round(v, 4) for k, v in run.items()}}))
+        return 0
+    if args.only == "prefill":
+        ms = prefill_timed(engine, 2048, vocab, repeats=max(1, args.steps))
+        print(json.dumps({"only": "prefill", "tokens": 2048, "ms": round(ms, 3)}))
+        return 0
     prefill_ms = prefill_timed(engine, 2048, vocab)
     flops = prefill_flops(raw, 2048)
     points = {}
