@@ -117,11 +117,26 @@ def _headers() -> List[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
 
 
+def _included_sources(path: str, seen: Optional[set] = None) -> List[str]:
+    """``.cu`` files of this folder that ``path`` pulls in with #include "..." (headers are always hashed)."""
+    seen = set() if seen is None else seen
+    with open(path) as fh:
+        for line in fh:
+            line = line.strip()
+            if line.startswith("#include \"") and line.endswith(".cu\""):
+                dep = os.path.join(CSRC, line[len("#include \""):-1])
+                if dep not in seen and os.path.isfile(dep):
+                    seen.add(dep)
+                    _included_sources(dep, seen)
+    return sorted(seen)
+
+
 def cuda_library_path(source: str, defines: Optional[Dict[str, object]] = None) -> str:
     defines = defines or {}
     src = os.path.join(CSRC, source)
     tag = "_".join(f"{k}{v}" for k, v in sorted(defines.items()))
-    digest = _hash([src] + _headers(), [repr(sorted(defines.items())), " ".join(ARCH_FLAGS + NVCC_FLAGS)])
+    digest = _hash([src] + _included_sources(src) + _headers(),
+                   [repr(sorted(defines.items())), " ".join(ARCH_FLAGS + NVCC_FLAGS)])
     stem = os.path.splitext(source)[0] + (f"_{tag}" if tag else "")
     return os.path.join(build_dir(), f"lib{stem}.{digest}.so")
 
@@ -163,8 +178,9 @@ def load_cuda_library(source: str, defines: Optional[Dict[str, object]] = None) 
 
 def all_cuda_libraries(head_dims: Iterable[int]) -> List[tuple]:
     """(source, defines) of every CUDA library that the package can ask for, attention for ``head_dims``."""
-    libs = [(f, None) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu") and f != "attention.cu"]
-    return libs + [("attention.cu", {"HEAD_DIM": int(d)}) for d in head_dims]
+    per_head = ("attention.cu", "decode_attention_static.cu")
+    libs = [(f, None) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu") and f not in per_head]
+    return libs + [(f, {"HEAD_DIM": int(d)}) for f in per_head for d in head_dims]
 
 
 def _host_sources() -> List[str]:
