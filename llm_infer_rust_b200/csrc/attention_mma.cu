@@ -1,0 +1,394 @@
+// Tensor-core attention over the paged bfloat16 cache, for one head size
+// (compile with -DHEAD_DIM=<multiple of 16, at most 256>).
+//
+// Decode (one query position per row) is bound by the bytes of keys and values
+// that a step has to read, so this kernel is built around the memory pipeline:
+// a CTA owns one (row, KV head, split of the keys); each of its warps walks its
+// own blocks of 32 keys through a private multi-stage cp.async ring (16 KB per
+// block and stage at head size 128), so that tens of KB per SM are in flight
+// without any block-wide barrier in the loop.  The arithmetic rides on
+// mma.sync m16n8k16 (bfloat16 in, float accumulate): the query heads that share
+// the KV head are the 16 rows of the A operand (at most 16 heads per KV head;
+// larger groups take the CUDA-core kernel), keys and values are read from
+// shared memory with ldmatrix (values transposed).  Scores, the running maximum,
+// the running sum and the output are float; probabilities are rounded to
+// bfloat16 only as the A operand of P.V, as the values themselves are bfloat16.
+//
+// Semantics are those of attention.cu (reference: src/models/attention/backend.rs:1455-1498):
+// KV head = head / group, score = q.k * scale, keys j <= p (and j > p - W with a
+// window), softmax in float, output = P.V.  Rows of a key block at or beyond the
+// sequence end are zero-filled, never read from the cache.
+#include <math.h>
+
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<head size, a multiple of 16>"
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "the tensor-core kernels take head sizes 16..256 in steps of 16");
+
+typedef __nv_bfloat16 bf16;
+constexpr int D = HEAD_DIM;
+constexpr int LD = D + 8;          // padded shared-memory row (16 bytes of padding): conflict-free ldmatrix
+constexpr int KB = 32;             // keys per block
+constexpr int QROWS = 16;          // rows of the A operand: query heads of one KV head
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- mbarrier and bulk-copy primitives (the copy engine writes shared memory and signals the barrier)
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Waits for a phase of the barrier, but never for ever: after about a second of polling it gives up,
+// flags the engine's error word and returns false (the caller's results are then meaningless, not hung).
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t start = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_ns() - start > 1000000000ull) {
+      atomicOr(err, B200_ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// One warp fetches keys [first_key, first_key + 32) of one KV head: lane r owns row r.  Its key row and
+// its value row (D bfloat16 = 2 D bytes each, contiguous in the cache) go to the padded tile rows with
+// one bulk copy each, which report to `bar`; a row at or beyond kv_end is zero-filled instead.
+__device__ __forceinline__ void fetch_block(bf16* ktile, bf16* vtile, const bf16* __restrict__ k_cache,
+                                            const bf16* __restrict__ v_cache, const int* __restrict__ table,
+                                            int page_size, int nkv, int kvh, int first_key, int kv_end,
+                                            uint64_t* bar, int lane) {
+  const int key = first_key + lane;
+  const int n_valid = min(KB, max(0, kv_end - first_key));
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads of the tile come before the copies
+  if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_valid) * 2u * D * sizeof(bf16));
+  __syncwarp();
+  if (key < kv_end) {
+    const int page = table[key / page_size];
+    const size_t row = (static_cast<size_t>(page) * page_size + key % page_size) * nkv + kvh;
+    bulk_copy_g2s(ktile + lane * LD, k_cache + row * D, D * sizeof(bf16), bar);
+    bulk_copy_g2s(vtile + lane * LD, v_cache + row * D, D * sizeof(bf16), bar);
+  } else {
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      *reinterpret_cast<uint4*>(ktile + lane * LD + c * 8) = zero;
+      *reinterpret_cast<uint4*>(vtile + lane * LD + c * 8) = zero;
+    }
+  }
+}
+
+// State of one warp: 16 query rows x D outputs in mma accumulator layout.
+struct WarpAcc {
+  float o[D / 8][4];
+  float m[2], l[2];          // rows lane/4 and lane/4 + 8; l is this thread's part of the row sum
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    m[0] = m[1] = -INFINITY; l[0] = l[1] = 0.0f;
+  }
+};
+
+// One block of 32 keys against the 16 query rows in `qs`.  `qpos0/1`: position of the query in rows
+// lane/4 and lane/4 + 8 (-1: the row is unused).  `scale_log2` = softmax scale * log2(e).
+__device__ __forceinline__ void block_mma(const bf16* qs, const bf16* ks, const bf16* vs, int first_key, int kv_end,
+                                          int window, int qpos0, int qpos1, float scale_log2, WarpAcc& st) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3, r8 = lane & 7;
+  float s[4][4];
+#pragma unroll
+  for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f; }
+#pragma unroll
+  for (int ks16 = 0; ks16 < D / 16; ++ks16) {
+    uint32_t a[4];
+    ldmatrix_x4(a, qs + (lane & 15) * LD + ks16 * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int n = 0; n < 4; n += 2) {
+      uint32_t b[4];
+      ldmatrix_x4(b, ks + (n * 8 + (mi >> 1) * 8 + r8) * LD + ks16 * 16 + (mi & 1) * 8);
+      mma_bf16(s[n], a, b[0], b[1]);
+      mma_bf16(s[n + 1], a, b[2], b[3]);
+    }
+  }
+  const int t2 = (lane & 3) * 2;
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = first_key + n * 8 + t2 + e;
+      const bool in_seq = key < kv_end;
+      const bool v0 = in_seq && qpos0 >= 0 && key <= qpos0 && (window <= 0 || key > qpos0 - window);
+      const bool v1 = in_seq && qpos1 >= 0 && key <= qpos1 && (window <= 0 || key > qpos1 - window);
+      s[n][e] = v0 ? s[n][e] * scale_log2 : -INFINITY;
+      s[n][2 + e] = v1 ? s[n][2 + e] * scale_log2 : -INFINITY;
+      mx0 = fmaxf(mx0, s[n][e]);
+      mx1 = fmaxf(mx1, s[n][2 + e]);
+    }
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float m0 = fmaxf(st.m[0], mx0), m1 = fmaxf(st.m[1], mx1);
+  const float c0 = m0 == -INFINITY ? 1.0f : exp2f(st.m[0] - m0);      // exp2(-inf) = 0 on the first visible block
+  const float c1 = m1 == -INFINITY ? 1.0f : exp2f(st.m[1] - m1);
+  const float base0 = m0 == -INFINITY ? 0.0f : m0, base1 = m1 == -INFINITY ? 0.0f : m1;
+  float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      s[n][e] = exp2f(s[n][e] - base0);              // a masked score is -inf: exp2 gives 0
+      s[n][2 + e] = exp2f(s[n][2 + e] - base1);
+      sum0 += s[n][e];
+      sum1 += s[n][2 + e];
+    }
+  }
+  st.m[0] = m0; st.m[1] = m1;
+  st.l[0] = st.l[0] * c0 + sum0;
+  st.l[1] = st.l[1] * c1 + sum1;
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { st.o[i][0] *= c0; st.o[i][1] *= c0; st.o[i][2] *= c1; st.o[i][3] *= c1; }
+#pragma unroll
+  for (int kk = 0; kk < 2; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dn = 0; dn < D / 8; dn += 2) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vs + (kk * 16 + (mi & 1) * 8 + r8) * LD + dn * 8 + (mi >> 1) * 8);
+      mma_bf16(st.o[dn], a, b[0], b[1]);
+      mma_bf16(st.o[dn + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ decoded tokens
+// grid (splits, nkv, decode rows).  Partials: part_acc[((row * nh + head) * splits + split) * D + dim]
+// (unnormalised), part_ml[...][2] = (maximum in log2 units, sum).
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                  bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                  const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
+                  const int* __restrict__ kv_len, const int* __restrict__ rows, int nh, int nkv, int page_size,
+                  int window, float scale_log2, int* err) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                    // [16][LD]
+  bf16* tiles = qs + QROWS * LD;                                   // [WARPS][STAGES][2][32][LD]
+  constexpr int TILE = 2 * KB * LD;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + static_cast<size_t>(WARPS) * STAGES * TILE);   // [WARPS][STAGES]
+
+  const int splits = gridDim.x, split = blockIdx.x, kvh = blockIdx.y;
+  const int row = rows[blockIdx.z];
+  const int group = nh / nkv, head0 = kvh * group;
+  const int tok = cu_q[row];
+  const int kv_end = kv_len[row];
+  const int qp = kv_end - 1;
+  int k_begin = window > 0 ? max(0, qp - window + 1) : 0;
+  k_begin -= k_begin % KB;
+  const int blocks_total = (kv_end - k_begin + KB - 1) / KB;
+  const int per_split = (blocks_total + splits - 1) / splits;
+  const int blk_lo = split * per_split, blk_hi = min(blocks_total, blk_lo + per_split);
+  const int* table = block_table + static_cast<size_t>(row) * table_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  for (int c = threadIdx.x; c < QROWS * (D / 8); c += blockDim.x) {
+    const int r = c / (D / 8), part = c - r * (D / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < group) v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(tok) * nh + head0 + r) * D + part * 8);
+    *reinterpret_cast<uint4*>(qs + r * LD + part * 8) = v;
+  }
+  if (threadIdx.x < WARPS * STAGES) mbar_init(bars + threadIdx.x, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  __syncthreads();
+  const int g = lane >> 2;
+  const int qpos0 = g < group ? qp : -1, qpos1 = g + 8 < group ? qp : -1;
+
+  bf16* my = tiles + static_cast<size_t>(warp) * STAGES * TILE;
+  uint64_t* my_bars = bars + warp * STAGES;
+  WarpAcc st;
+  st.init();
+  int issue = blk_lo + warp;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (issue < blk_hi)
+      fetch_block(my + s * TILE, my + s * TILE + KB * LD, k_cache, v_cache, table, page_size, nkv, kvh,
+                  k_begin + issue * KB, kv_end, my_bars + s, lane);
+    issue += WARPS;
+  }
+  int stage = 0;
+  uint32_t parity = 0;
+  for (int blk = blk_lo + warp; blk < blk_hi; blk += WARPS) {
+    const int s_issue = stage == 0 ? STAGES - 1 : stage - 1;      // the stage that the previous block left
+    if (issue < blk_hi)
+      fetch_block(my + s_issue * TILE, my + s_issue * TILE + KB * LD, k_cache, v_cache, table, page_size, nkv, kvh,
+                  k_begin + issue * KB, kv_end, my_bars + s_issue, lane);
+    issue += WARPS;
+    if (!mbar_wait(my_bars + stage, parity, err)) {
+      // Give the copies that are still in flight a bounded time to land before the tiles are reused.
+      for (int s = 0; s < STAGES; ++s) mbar_wait(my_bars + s, s < stage ? parity ^ 1u : parity, err);
+      break;
+    }
+    __syncwarp();                                      // zero-filled rows of other lanes are visible
+    const bf16* t = my + stage * TILE;
+    block_mma(qs, t, t + KB * LD, k_begin + blk * KB, kv_end, window, qpos0, qpos1, scale_log2, st);
+    __syncwarp();                                      // every lane is done reading before the stage is refilled
+    if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+  }
+  st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
+  st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
+  __syncthreads();
+  // Merge the warps through shared memory: [WARPS][group][D + 2] floats over the tile area.
+  float* merge = reinterpret_cast<float*>(tiles);
+  constexpr int MS = D + 2;
+  const int t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half;
+    if (r < group) {
+      float* dst = merge + (warp * group + r) * MS;
+#pragma unroll
+      for (int dn = 0; dn < D / 8; ++dn) {
+        dst[dn * 8 + t2] = st.o[dn][2 * half];
+        dst[dn * 8 + t2 + 1] = st.o[dn][2 * half + 1];
+      }
+      if ((lane & 3) == 0) { dst[D] = st.m[half]; dst[D + 1] = st.l[half]; }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < group * D; i += blockDim.x) {
+    const int r = i / D, dim = i - r * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge[(w * group + r) * MS + D]);
+    float l = 0.0f, o = 0.0f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float* src = merge + (w * group + r) * MS;
+        const float f = exp2f(src[D] - m);
+        l += src[D + 1] * f;
+        o += src[dim] * f;
+      }
+    }
+    const int head = head0 + r;
+    if (splits == 1) {
+      out[(static_cast<size_t>(tok) * nh + head) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+    } else {
+      const size_t slot = (static_cast<size_t>(blockIdx.z) * nh + head) * splits + split;
+      part_acc[slot * D + dim] = o;
+      if (dim == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+    }
+  }
+}
+
+// grid (decode rows, nh): combines the splits of one head (maxima are in log2 units).
+__global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
+                                        const float* __restrict__ part_ml, const int* __restrict__ cu_q,
+                                        const int* __restrict__ rows, int nh, int splits) {
+  const int head = blockIdx.y;
+  const int tok = cu_q[rows[blockIdx.x]];
+  const size_t base = (static_cast<size_t>(blockIdx.x) * nh + head) * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
+    float l = 0.0f, o = 0.0f;
+    if (m != -INFINITY) {
+      for (int s = 0; s < splits; ++s) {
+        const float f = exp2f(part_ml[(base + s) * 2] - m);
+        l += part_ml[(base + s) * 2 + 1] * f;
+        o += part_acc[(base + s) * D + dim] * f;
+      }
+    }
+    out[(static_cast<size_t>(tok) * nh + head) * D + dim] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
+  }
+}
+
+// ------------------------------------------------------------------ launchers
+constexpr size_t kSmemLimit = 226 * 1024;
+constexpr size_t kTileBytes = 2 * KB * LD * sizeof(bf16);
+constexpr size_t kQBytes = QROWS * LD * sizeof(bf16);
+// Four warps with three stages where that fits shared memory, else fewer stages, else fewer warps.
+constexpr size_t kBarBytes = 256;
+constexpr int kWarps = kQBytes + kBarBytes + 4 * 2 * kTileBytes <= kSmemLimit ? 4 : 2;
+constexpr int kStages = kQBytes + kBarBytes + kWarps * 3 * kTileBytes <= kSmemLimit ? 3 : 2;
+static_assert(kQBytes + kBarBytes + kWarps * kStages * kTileBytes <= kSmemLimit, "the key blocks must fit shared memory");
+static_assert(kWarps * kStages * sizeof(uint64_t) <= kBarBytes, "barriers");
+
+B200_EXPORT int b200_attention_mma_head_dim() { return D; }
+B200_EXPORT int b200_attention_mma_max_group() { return QROWS; }
+
+// Same arguments as b200_decode_attention of attention.cu; bfloat16 only, at most 16 query heads per KV head.
+B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          float* scratch, const int* block_table, int table_stride,
+                                          const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
+                                          int nkv, int page_size, int window, float scale, int splits,
+                                          int* err, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
+  // The merge area ([warps][group][D + 2] floats) lies over the tiles and is smaller than they are.
+  constexpr size_t smem = kQBytes + kWarps * kStages * kTileBytes + kBarBytes;
+  static_assert(static_cast<size_t>(kWarps) * QROWS * (D + 2) * sizeof(float) <= kWarps * kStages * kTileBytes, "merge area");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  float* part_acc = scratch;
+  float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
+  dim3 grid(splits, nkv, n_rows);
+  decode_mma_kernel<kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
+      static_cast<const bf16*>(q), static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache),
+      static_cast<bf16*>(out), part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size,
+      window, scale * 1.4426950408889634f, err);
+  int rc = b200_check_launch();
+  if (rc != 0 || splits == 1) return rc;
+  dim3 mgrid(n_rows, nh);
+  decode_mma_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(static_cast<bf16*>(out), part_acc, part_ml, cu_q,
+                                                                    rows, nh, splits);
+  return b200_check_launch();
+}

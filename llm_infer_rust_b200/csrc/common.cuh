@@ -15,6 +15,7 @@ enum : int {
   B200_ERR_SLOT_RANGE = 2,       // cache slot outside the pool
   B200_ERR_POSITION_RANGE = 4,   // position beyond the rotary table
   B200_ERR_SAMPLING = 8,         // no valid token could be drawn
+  B200_ERR_WAIT_TIMEOUT = 16,    // a bounded wait inside a kernel ran out
 };
 
 // return codes of launchers: 0 ok, > 0 a cudaError_t, < 0 refused arguments

@@ -18,7 +18,8 @@ from .build import load_cuda_library
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 ERROR_BITS = {1: "a token id outside the embedding table", 2: "a cache slot outside the pool",
-              4: "a position beyond the rotary table", 8: "sampling found no valid token"}
+              4: "a position beyond the rotary table", 8: "sampling found no valid token",
+              16: "a bounded wait inside a kernel ran out"}
 _RC = {-1: "unsupported dtype", -2: "a size the kernel refuses", -3: "misaligned pointer"}
 
 
@@ -231,6 +232,28 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     _ok(rc, "prefill_attention")
 
 
+MMA_MAX_GROUP = 16
+MMA_MAX_HEAD_DIM = 256
+
+
+def _attention_mma(head_dim: int):
+    return load_cuda_library("attention_mma.cu", {"HEAD_DIM": head_dim})
+
+
+def decode_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """bfloat16 caches with at most 16 query heads per KV head and heads up to 256 wide take the
+    tensor-core kernel; everything else (float32, wider groups or heads) the all-sizes kernel."""
+    return (dtype == torch.bfloat16 and num_heads // num_kv_heads <= MMA_MAX_GROUP
+            and head_dim <= MMA_MAX_HEAD_DIM and head_dim % 16 == 0)
+
+
+def decode_ctas_per_split(dtype: torch.dtype, n_rows: int, num_heads: int, num_kv_heads: int, head_dim: int) -> int:
+    """CTAs that the decode kernel launches for each split of the keys."""
+    if decode_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
+        return n_rows * num_kv_heads
+    return n_rows * num_kv_heads * ((num_heads // num_kv_heads + 3) // 4)
+
+
 def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: int) -> int:
     return 0 if splits <= 1 else n_rows * num_heads * splits * (head_dim + 2)
 
@@ -247,6 +270,13 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     need = decode_scratch_floats(n_rows, num_heads, head_dim, splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
+    if decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim):
+        rc = _attention_mma(head_dim).b200_decode_attention_mma(
+            _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
+            _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
+            ctypes.c_float(scale), splits, _p(error_word(q.device)), _stream())
+        _ok(rc, "decode_attention_mma", 2 if splits > 1 else 1)
+        return
     rc = _attention(head_dim).b200_decode_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
         _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),

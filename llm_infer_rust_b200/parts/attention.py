@@ -9,17 +9,24 @@ from ..kernels import ops
 from .base import PagedKVSpec, ParamDecl, Part
 from .registry import register_part
 
-# Resident CTAs that the split-KV decode kernel aims for per SM.
-_DECODE_CTAS_PER_SM = 2
-_DECODE_KEYS_PER_CTA = 128      # 4 warps x one block of 32 keys
+_KEYS_PER_CTA_AT_LEAST = 512      # fewer keys per CTA leave its warps' copy pipelines half empty
 
 
-def decode_splits(n_rows: int, num_kv_heads: int, group: int, kv_len_bound: int, sm_count: int) -> int:
-    """How many CTAs share one row's keys: enough to fill the GPU, never more than there are key blocks."""
-    per_split_ctas = max(1, n_rows * num_kv_heads * ((group + 3) // 4))
-    want = -(-sm_count * _DECODE_CTAS_PER_SM // per_split_ctas)
-    most = max(1, -(-kv_len_bound // _DECODE_KEYS_PER_CTA))
-    return max(1, min(want, most, 64))
+def decode_splits(ctas_per_split: int, kv_len_bound: int, sm_count: int) -> int:
+    """How many CTAs share one row's keys.
+
+    With ``ctas_per_split`` CTAs for each split, the number of splits is chosen so that the
+    grid fills whole waves of SMs as well as it can while every CTA keeps at least 512 keys.
+    """
+    ctas_per_split = max(1, ctas_per_split)
+    most = max(1, min(64, kv_len_bound // _KEYS_PER_CTA_AT_LEAST))
+    best, best_fill = 1, 0.0
+    for splits in range(1, most + 1):
+        ctas = ctas_per_split * splits
+        fill = ctas / (sm_count * -(-ctas // sm_count))
+        if fill > best_fill * 1.05:
+            best, best_fill = splits, fill
+    return best
 
 
 class GQAttention(Part):
@@ -87,7 +94,8 @@ class GQAttention(Part):
                                   self.nh, self.nkv, self.d, page, self.window, self.scale)
         if ctx.num_decode:
             bound = min(ctx.kv_len_bound, self.window) if self.window else ctx.kv_len_bound
-            splits = decode_splits(ctx.num_decode, self.nkv, self.nh // self.nkv, bound, ctx.sm_count)
+            per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, self.nh, self.nkv, self.d)
+            splits = decode_splits(per_split, bound, ctx.sm_count)
             need = ops.decode_scratch_floats(ctx.num_decode, self.nh, self.d, splits)
             scratch = ctx.scratch(need) if need else None
             ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
