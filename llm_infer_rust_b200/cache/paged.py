@@ -5,8 +5,9 @@ Host bookkeeping (which page holds what) lives in the C++ ``CacheManager``
 sizes the pools and owns the tensors.
 
 Grouping.  Every entry of the model's run list that keeps keys and values gets
-tensors of its own, K and V of shape [pages + 1, page_size, kv_heads, head_dim]
-(page 0 is the sink).  Entries whose mixers have the same NEED form a group: all
+tensors of its own, K and V of shape [pages + 1, kv_heads, page_size, head_dim]
+(page 0 is the sink; the rows of one page and KV head are contiguous, so that the
+copy engine fetches them as one block).  Entries whose mixers have the same NEED form a group: all
 keys, or a window of W positions.  A group has its own page pool and every
 request its own block table in it, so that a windowed group can give pages back
 while the request runs.  Entries of one group may differ in head count and head
@@ -32,7 +33,7 @@ from ..kernels.build import load_host_runtime
 class LayerCache:
     """The cache of one entry of the run list."""
     group: int = -1                          # cache group of the pages, -1: no paged cache
-    k: Optional[torch.Tensor] = None         # [pages + 1, page_size, kv_heads, head_dim]
+    k: Optional[torch.Tensor] = None         # [pages + 1, kv_heads, page_size, head_dim]
     v: Optional[torch.Tensor] = None
     writes: bool = True                      # False: this entry reads another entry's pages
     state: Optional[torch.Tensor] = None     # [slots + 1, *state_shape]; slot 0 is the sink
@@ -145,7 +146,7 @@ class PagedCache:
                 g = plan.group_of_entry[e]
                 cache.group = g
                 if entry.reads is None:
-                    shape = (plan.groups[g].num_pages + 1, plan.groups[g].page_size, kv.num_kv_heads, kv.head_dim)
+                    shape = (plan.groups[g].num_pages + 1, kv.num_kv_heads, plan.groups[g].page_size, kv.head_dim)
                     cache.k = torch.zeros(shape, dtype=dtype, device=device)
                     cache.v = torch.zeros(shape, dtype=dtype, device=device)
                     owned[e] = cache

@@ -144,9 +144,9 @@ __device__ __forceinline__ void load_key_block(T* dst, const T* __restrict__ cac
     const bool valid = key < kv_end;
     const T* src = cache;
     if (valid) {
-      const int page = table[key / page_size];
-      const size_t slot = static_cast<size_t>(page) * page_size + key % page_size;
-      src = cache + (slot * nkv + kvh) * D + part * G::CHUNK;
+      const int page = table[key / page_size];       // cache[page][kv head][offset in page][D]
+      const size_t row = (static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size;
+      src = cache + row * D + part * G::CHUNK;
     }
     cp_async16(dst + r * G::STRIDE + part * G::CHUNK, src, valid);
   }

@@ -2,23 +2,32 @@
 // (compile with -DHEAD_DIM=<multiple of 16, at most 256>).
 //
 // Decode (one query position per row) is bound by the bytes of keys and values
-// that a step has to read, so this kernel is built around the memory pipeline:
-// a CTA owns one (row, KV head, split of the keys); each of its warps walks its
-// own blocks of 32 keys through a private multi-stage cp.async ring (16 KB per
-// block and stage at head size 128), so that tens of KB per SM are in flight
-// without any block-wide barrier in the loop.  The arithmetic rides on
-// mma.sync m16n8k16 (bfloat16 in, float accumulate): the query heads that share
-// the KV head are the 16 rows of the A operand (at most 16 heads per KV head;
-// larger groups take the CUDA-core kernel), keys and values are read from
-// shared memory with ldmatrix (values transposed).  Scores, the running maximum,
-// the running sum and the output are float; probabilities are rounded to
+// that a step has to read, so this kernel is built around the copy engine.  The
+// cache is laid out [page][KV head][offset in page][head_dim]: the rows of one
+// page and KV head are one contiguous block, which TMA fetches as boxes of
+// (up to 32 rows) x (64 dims = 128 bytes) straight into shared memory in the
+// 128-byte swizzle, reporting to an mbarrier.  A CTA owns one (row, KV head,
+// split of the keys); each of its warps walks its own blocks of 32 keys through a
+// private ring of stages (16 KB per block at head size 128), so that tens of KB
+// per SM are in flight and the loop has no block-wide barrier.  Every wait on a
+// barrier is bounded by the clock: when it runs out the kernel flags the engine's
+// error word, gives the outstanding copies a bounded time to land and returns.
+// The arithmetic rides on mma.sync m16n8k16 (bfloat16 in, float accumulate): the
+// query heads that share the KV head are the 16 rows of the A operand (at most 16
+// heads per KV head; larger groups, page sizes that are no power of two and float
+// caches take the CUDA-core kernel of attention.cu), keys and values are read
+// from the swizzled tiles with ldmatrix (values transposed).  Scores, the running
+// maximum, the running sum and the output are float; probabilities are rounded to
 // bfloat16 only as the A operand of P.V, as the values themselves are bfloat16.
 //
 // Semantics are those of attention.cu (reference: src/models/attention/backend.rs:1455-1498):
 // KV head = head / group, score = q.k * scale, keys j <= p (and j > p - W with a
-// window), softmax in float, output = P.V.  Rows of a key block at or beyond the
-// sequence end are zero-filled, never read from the cache.
+// window), softmax in float, output = P.V.  Value rows at or beyond the sequence
+// end are zeroed in shared memory before they are used, key rows there are masked:
+// a page that is used again may hold anything.
+#include <cuda.h>
 #include <math.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -29,8 +38,11 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "the tens
 
 typedef __nv_bfloat16 bf16;
 constexpr int D = HEAD_DIM;
-constexpr int LD = D + 8;          // padded shared-memory row (16 bytes of padding): conflict-free ldmatrix
+constexpr int LD = D + 8;          // padded row of the query tile (16 bytes of padding): conflict-free ldmatrix
 constexpr int KB = 32;             // keys per block
+constexpr int NB = (D + 63) / 64;  // 64-dim (128-byte) column boxes per row
+constexpr int HALF_BYTES = KB * 128;              // one column box of a block: 32 rows x 128 bytes
+constexpr int TILE_BYTES = 2 * NB * HALF_BYTES;   // keys then values of one block
 constexpr int QROWS = 16;          // rows of the A operand: query heads of one KV head
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -85,36 +97,45 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   }
   return true;
 }
-__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
-// One warp fetches keys [first_key, first_key + 32) of one KV head: lane r owns row r.  Its key row and
-// its value row (D bfloat16 = 2 D bytes each, contiguous in the cache) go to the padded tile rows with
-// one bulk copy each, which report to `bar`; a row at or beyond kv_end is zero-filled instead.
-__device__ __forceinline__ void fetch_block(bf16* ktile, bf16* vtile, const bf16* __restrict__ k_cache,
-                                            const bf16* __restrict__ v_cache, const int* __restrict__ table,
-                                            int page_size, int nkv, int kvh, int first_key, int kv_end,
-                                            uint64_t* bar, int lane) {
-  const int key = first_key + lane;
-  const int n_valid = min(KB, max(0, kv_end - first_key));
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads of the tile come before the copies
-  if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_valid) * 2u * D * sizeof(bf16));
+// Byte offset of (row r, 16-byte chunk c of the row's D dims) inside a tile of NB column boxes, each
+// [32 rows][128 bytes] in the 128-byte swizzle (chunk index XOR row mod 8; tiles are 1024-byte aligned).
+__device__ __forceinline__ int swz(int r, int c) {
+  return (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+
+// One warp fetches keys [first_key, first_key + 32) of one KV head into `tile` (keys, then values).
+// The block is cut into sub-blocks of `box_rows` rows (a power of two that divides 32 and the page
+// size, so a sub-block never leaves its page); lane j issues the boxes of sub-block j with the page
+// id `page` that it looked up one block earlier.  Sub-blocks that start at or beyond kv_end are skipped.
+__device__ __forceinline__ void fetch_block(unsigned char* tile, const CUtensorMap* kmap, const CUtensorMap* vmap,
+                                            int page, int page_size, int nkv, int kvh, int box_rows, int first_key,
+                                            int kv_end, uint64_t* bar, int lane) {
+  const int n_sub = (min(KB, kv_end - first_key) + box_rows - 1) / box_rows;
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // earlier reads and writes of the tile come first
+  if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * NB * box_rows * 128u);
   __syncwarp();
-  if (key < kv_end) {
-    const int page = table[key / page_size];
-    const size_t row = (static_cast<size_t>(page) * page_size + key % page_size) * nkv + kvh;
-    bulk_copy_g2s(ktile + lane * LD, k_cache + row * D, D * sizeof(bf16), bar);
-    bulk_copy_g2s(vtile + lane * LD, v_cache + row * D, D * sizeof(bf16), bar);
-  } else {
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  if (lane < n_sub) {
+    const int key0 = first_key + lane * box_rows;
+    const int y = (page * nkv + kvh) * page_size + key0 % page_size;
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
-      *reinterpret_cast<uint4*>(ktile + lane * LD + c * 8) = zero;
-      *reinterpret_cast<uint4*>(vtile + lane * LD + c * 8) = zero;
+    for (int h = 0; h < NB; ++h) {
+      tma_load_2d(tile + h * HALF_BYTES + lane * box_rows * 128, kmap, h * 64, y, bar);
+      tma_load_2d(tile + (NB + h) * HALF_BYTES + lane * box_rows * 128, vmap, h * 64, y, bar);
     }
   }
+}
+
+// Page id of the sub-block that this lane fetches in the block that starts at first_key.  It is loaded one
+// block ahead of its use, so that the table's latency is off the copies' critical path.
+__device__ __forceinline__ int lane_page(const int* __restrict__ table, int page_size, int box_rows, int first_key,
+                                         int kv_end, int lane) {
+  const int key0 = first_key + lane * box_rows;
+  return (lane * box_rows < KB && key0 < kv_end) ? table[key0 / page_size] : 0;
 }
 
 // State of one warp: 16 query rows x D outputs in mma accumulator layout.
@@ -130,7 +151,7 @@ struct WarpAcc {
 
 // One block of 32 keys against the 16 query rows in `qs`.  `qpos0/1`: position of the query in rows
 // lane/4 and lane/4 + 8 (-1: the row is unused).  `scale_log2` = softmax scale * log2(e).
-__device__ __forceinline__ void block_mma(const bf16* qs, const bf16* ks, const bf16* vs, int first_key, int kv_end,
+__device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* ks, const unsigned char* vs, int first_key, int kv_end,
                                           int window, int qpos0, int qpos1, float scale_log2, WarpAcc& st) {
   const int lane = threadIdx.x & 31;
   const int mi = lane >> 3, r8 = lane & 7;
@@ -144,7 +165,7 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const bf16* ks, const 
 #pragma unroll
     for (int n = 0; n < 4; n += 2) {
       uint32_t b[4];
-      ldmatrix_x4(b, ks + (n * 8 + (mi >> 1) * 8 + r8) * LD + ks16 * 16 + (mi & 1) * 8);
+      ldmatrix_x4(b, ks + swz(n * 8 + (mi >> 1) * 8 + r8, ks16 * 2 + (mi & 1)));
       mma_bf16(s[n], a, b[0], b[1]);
       mma_bf16(s[n + 1], a, b[2], b[3]);
     }
@@ -197,7 +218,7 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const bf16* ks, const 
 #pragma unroll
     for (int dn = 0; dn < D / 8; dn += 2) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, vs + (kk * 16 + (mi & 1) * 8 + r8) * LD + dn * 8 + (mi >> 1) * 8);
+      ldmatrix_x4_trans(b, vs + swz(kk * 16 + (mi & 1) * 8 + r8, dn + (mi >> 1)));
       mma_bf16(st.o[dn], a, b[0], b[1]);
       mma_bf16(st.o[dn + 1], a, b[2], b[3]);
     }
@@ -207,18 +228,18 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const bf16* ks, const 
 // ------------------------------------------------------------------ decoded tokens
 // grid (splits, nkv, decode rows).  Partials: part_acc[((row * nh + head) * splits + split) * D + dim]
 // (unnormalised), part_ml[...][2] = (maximum in log2 units, sum).
+// Shared memory: [WARPS][STAGES] tiles (1024-byte aligned), the query tile [16][LD], the barriers.
 template <int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32, 1)
-decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                  bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                  const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
-                  const int* __restrict__ kv_len, const int* __restrict__ rows, int nh, int nkv, int page_size,
-                  int window, float scale_log2, int* err) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                    // [16][LD]
-  bf16* tiles = qs + QROWS * LD;                                   // [WARPS][STAGES][2][32][LD]
-  constexpr int TILE = 2 * KB * LD;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + static_cast<size_t>(WARPS) * STAGES * TILE);   // [WARPS][STAGES]
+decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                  const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_acc,
+                  float* __restrict__ part_ml, const int* __restrict__ block_table, int table_stride,
+                  const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ rows, int nh,
+                  int nkv, int page_size, int box_rows, int window, float scale_log2, int* err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  bf16* qs = reinterpret_cast<bf16*>(tiles + static_cast<size_t>(WARPS) * STAGES * TILE_BYTES);   // [16][LD]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(qs + QROWS * LD);                                   // [WARPS][STAGES]
 
   const int splits = gridDim.x, split = blockIdx.x, kvh = blockIdx.y;
   const int row = rows[blockIdx.z];
@@ -246,34 +267,48 @@ decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
   const int g = lane >> 2;
   const int qpos0 = g < group ? qp : -1, qpos1 = g + 8 < group ? qp : -1;
 
-  bf16* my = tiles + static_cast<size_t>(warp) * STAGES * TILE;
+  unsigned char* my = tiles + static_cast<size_t>(warp) * STAGES * TILE_BYTES;
   uint64_t* my_bars = bars + warp * STAGES;
   WarpAcc st;
   st.init();
   int issue = blk_lo + warp;
+  int page = issue < blk_hi ? lane_page(table, page_size, box_rows, k_begin + issue * KB, kv_end, lane) : 0;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
+    const int next = issue + WARPS;
+    const int next_page = next < blk_hi ? lane_page(table, page_size, box_rows, k_begin + next * KB, kv_end, lane) : 0;
     if (issue < blk_hi)
-      fetch_block(my + s * TILE, my + s * TILE + KB * LD, k_cache, v_cache, table, page_size, nkv, kvh,
-                  k_begin + issue * KB, kv_end, my_bars + s, lane);
-    issue += WARPS;
+      fetch_block(my + s * TILE_BYTES, &kmap, &vmap, page, page_size, nkv, kvh, box_rows, k_begin + issue * KB, kv_end,
+                  my_bars + s, lane);
+    issue = next;
+    page = next_page;
   }
   int stage = 0;
   uint32_t parity = 0;
   for (int blk = blk_lo + warp; blk < blk_hi; blk += WARPS) {
     const int s_issue = stage == 0 ? STAGES - 1 : stage - 1;      // the stage that the previous block left
+    const int next = issue + WARPS;
+    const int next_page = next < blk_hi ? lane_page(table, page_size, box_rows, k_begin + next * KB, kv_end, lane) : 0;
     if (issue < blk_hi)
-      fetch_block(my + s_issue * TILE, my + s_issue * TILE + KB * LD, k_cache, v_cache, table, page_size, nkv, kvh,
-                  k_begin + issue * KB, kv_end, my_bars + s_issue, lane);
-    issue += WARPS;
+      fetch_block(my + s_issue * TILE_BYTES, &kmap, &vmap, page, page_size, nkv, kvh, box_rows, k_begin + issue * KB,
+                  kv_end, my_bars + s_issue, lane);
+    issue = next;
+    page = next_page;
     if (!mbar_wait(my_bars + stage, parity, err)) {
       // Give the copies that are still in flight a bounded time to land before the tiles are reused.
       for (int s = 0; s < STAGES; ++s) mbar_wait(my_bars + s, s < stage ? parity ^ 1u : parity, err);
       break;
     }
-    __syncwarp();                                      // zero-filled rows of other lanes are visible
-    const bf16* t = my + stage * TILE;
-    block_mma(qs, t, t + KB * LD, k_begin + blk * KB, kv_end, window, qpos0, qpos1, scale_log2, st);
+    unsigned char* t = my + stage * TILE_BYTES;
+    const int first_key = k_begin + blk * KB;
+    if (first_key + KB > kv_end && first_key + lane >= kv_end) {
+      // Value rows beyond the sequence: whatever the page holds there must not reach P.V.
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
+    }
+    __syncwarp();
+    block_mma(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, scale_log2, st);
     __syncwarp();                                      // every lane is done reading before the stage is refilled
     if (++stage == STAGES) { stage = 0; parity ^= 1u; }
   }
@@ -281,7 +316,7 @@ decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, 
   st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
   __syncthreads();
   // Merge the warps through shared memory: [WARPS][group][D + 2] floats over the tile area.
-  float* merge = reinterpret_cast<float*>(tiles);
+  float* merge = reinterpret_cast<float*>(tiles);     // all copies have landed and been used
   constexpr int MS = D + 2;
   const int t2 = (lane & 3) * 2;
 #pragma unroll
@@ -348,29 +383,65 @@ __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __r
 
 // ------------------------------------------------------------------ launchers
 constexpr size_t kSmemLimit = 226 * 1024;
-constexpr size_t kTileBytes = 2 * KB * LD * sizeof(bf16);
 constexpr size_t kQBytes = QROWS * LD * sizeof(bf16);
-// Four warps with three stages where that fits shared memory, else fewer stages, else fewer warps.
 constexpr size_t kBarBytes = 256;
-constexpr int kWarps = kQBytes + kBarBytes + 4 * 2 * kTileBytes <= kSmemLimit ? 4 : 2;
-constexpr int kStages = kQBytes + kBarBytes + kWarps * 3 * kTileBytes <= kSmemLimit ? 3 : 2;
-static_assert(kQBytes + kBarBytes + kWarps * kStages * kTileBytes <= kSmemLimit, "the key blocks must fit shared memory");
+constexpr size_t kFixedBytes = 1024 + kQBytes + kBarBytes;            // alignment slack, query tile, barriers
+// Six warps with two stages where that fits shared memory (head sizes up to 128), else four, else two.
+constexpr int kWarps = kFixedBytes + 6 * 2 * TILE_BYTES <= kSmemLimit ? 6 : (kFixedBytes + 4 * 2 * TILE_BYTES <= kSmemLimit ? 4 : 2);
+constexpr int kStages = kFixedBytes + kWarps * 3 * TILE_BYTES <= kSmemLimit ? 3 : 2;
+static_assert(kFixedBytes + kWarps * kStages * TILE_BYTES <= kSmemLimit, "the key blocks must fit shared memory");
 static_assert(kWarps * kStages * sizeof(uint64_t) <= kBarBytes, "barriers");
+static_assert(static_cast<size_t>(kWarps) * QROWS * (D + 2) * sizeof(float) <= static_cast<size_t>(kWarps) * kStages * TILE_BYTES,
+              "the merge area lies over the tiles");
 
 B200_EXPORT int b200_attention_mma_head_dim() { return D; }
 B200_EXPORT int b200_attention_mma_max_group() { return QROWS; }
 
-// Same arguments as b200_decode_attention of attention.cu; bfloat16 only, at most 16 query heads per KV head.
-B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Writes into `out_map` (128 bytes) the TMA descriptor of one cache tensor [pages + 1, kv_heads, page_size, D]
+// seen as a matrix of `rows` = (pages + 1) * kv_heads * page_size rows of D bfloat16, fetched in boxes of
+// `box_rows` rows x 64 columns with the 128-byte swizzle.  Columns beyond D read as zeros.
+B200_EXPORT int b200_kv_tensor_map(void* out_map, const void* cache, long long rows, int box_rows) {
+  if (rows <= 0 || box_rows <= 0 || box_rows > 256) return B200_BAD_SIZE;
+  if (reinterpret_cast<uintptr_t>(cache) % 16 != 0) return B200_BAD_ALIGN;
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (fn == nullptr || found != cudaDriverEntryPointSuccess) return static_cast<int>(cudaErrorNotSupported);
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * sizeof(bf16)};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem_strides,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 1000 + static_cast<int>(r);
+  memcpy(out_map, &map, sizeof(map));
+  return 0;
+}
+
+// Decoded tokens over a bfloat16 cache.  `k_map`, `v_map`: descriptors from b200_kv_tensor_map with
+// box_rows = min(page_size, 32); page_size must be a power of two; at most 16 query heads per KV head.
+// `scratch` as for b200_decode_attention of attention.cu.
+B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, const void* v_map, void* out,
                                           float* scratch, const int* block_table, int table_stride,
                                           const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                           int nkv, int page_size, int window, float scale, int splits,
                                           int* err, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
-  // The merge area ([warps][group][D + 2] floats) lies over the tiles and is smaller than they are.
-  constexpr size_t smem = kQBytes + kWarps * kStages * kTileBytes + kBarBytes;
-  static_assert(static_cast<size_t>(kWarps) * QROWS * (D + 2) * sizeof(float) <= kWarps * kStages * kTileBytes, "merge area");
+  if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
+  const int box_rows = page_size < KB ? page_size : KB;
+  constexpr size_t smem = kFixedBytes + static_cast<size_t>(kWarps) * kStages * TILE_BYTES;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<kWarps, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -378,13 +449,15 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_cache, co
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
+  CUtensorMap kmap, vmap;
+  memcpy(&kmap, k_map, sizeof(kmap));
+  memcpy(&vmap, v_map, sizeof(vmap));
   float* part_acc = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
   dim3 grid(splits, nkv, n_rows);
   decode_mma_kernel<kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
-      static_cast<const bf16*>(q), static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache),
-      static_cast<bf16*>(out), part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size,
-      window, scale * 1.4426950408889634f, err);
+      kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table, table_stride,
+      cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
   int rc = b200_check_launch();
   if (rc != 0 || splits == 1) return rc;
   dim3 mgrid(n_rows, nh);

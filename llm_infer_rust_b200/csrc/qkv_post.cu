@@ -6,7 +6,7 @@
 // Reference semantics: src/layers/fused_ops.cu:69-87 (per-head norm, float sum
 // of squares, rsqrt(mean + eps) * weight), :108-133 (rotation in float from a
 // float cos/sin table, pairs (i, i + rot/2)), src/models/attention/kv_store.cu:7-33
-// (copy to cache[slot], slot 0 is skipped).  The reference runs three kernels
+// (copy to the row of cache slot = page * page_size + offset; slot 0 is skipped).  The reference runs three kernels
 // and rounds after the norm and again after the rotation; here both happen in
 // float and the value is rounded once.  A position beyond the table or a slot
 // outside the pool sets an error bit and the access is skipped (the reference
@@ -23,7 +23,7 @@ __global__ void qkv_post_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_o
                                 const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                 int rot_dim, int max_pos, const int* __restrict__ positions,
                                 const int* __restrict__ slots, int tokens, int nh, int nkv, int d,
-                                long long cache_slots, int* err) {
+                                int page_size, long long cache_slots, int* err) {
   __shared__ float buf[WARPS][MAX_HEAD_DIM];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int heads = nh + 2 * nkv;
@@ -46,7 +46,9 @@ __global__ void qkv_post_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_o
       return;
     }
     const int kvh = is_k ? h - nh : h - nh - nkv;
-    dst = (is_k ? k_cache : v_cache) + (static_cast<size_t>(slot) * nkv + kvh) * d;
+    // cache[page][kv head][offset in page][d]: a page's rows of one KV head are contiguous
+    const int page = slot / page_size, offset = slot - page * page_size;
+    dst = (is_k ? k_cache : v_cache) + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * d;
   }
   if (!is_q && !is_k) {                           // v: a plain copy
     for (int i = lane; i < d; i += 32) dst[i] = src[i];
@@ -94,10 +96,10 @@ __global__ void qkv_post_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_o
 B200_EXPORT int b200_qkv_post(const void* qkv, void* q_out, void* k_cache, void* v_cache, const void* q_w,
                               const void* k_w, float eps, const float* cos_table, const float* sin_table,
                               int rot_dim, int max_pos, const int* positions, const int* slots, int tokens,
-                              int nh, int nkv, int d, long long cache_slots, int act_dtype, int w_dtype,
+                              int nh, int nkv, int d, int page_size, long long cache_slots, int act_dtype, int w_dtype,
                               int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (d <= 0 || d > MAX_HEAD_DIM || nh <= 0 || nkv <= 0) return B200_BAD_SIZE;
+  if (d <= 0 || d > MAX_HEAD_DIM || nh <= 0 || nkv <= 0 || page_size <= 0) return B200_BAD_SIZE;
   if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return B200_BAD_SIZE;
   const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
   const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
@@ -105,7 +107,7 @@ B200_EXPORT int b200_qkv_post(const void* qkv, void* q_out, void* k_cache, void*
   qkv_post_kernel<TA, TW><<<blocks, WARPS * 32, 0, stream>>>(                                          \
       static_cast<const TA*>(qkv), static_cast<TA*>(q_out), static_cast<TA*>(k_cache),                 \
       static_cast<TA*>(v_cache), static_cast<const TW*>(q_w), static_cast<const TW*>(k_w), eps,        \
-      cos_table, sin_table, rot_dim, max_pos, positions, slots, tokens, nh, nkv, d, cache_slots, err)
+      cos_table, sin_table, rot_dim, max_pos, positions, slots, tokens, nh, nkv, d, page_size, cache_slots, err)
   if (act_dtype == B200_F32 && w_dtype == B200_F32) { CALL(float, float); }
   else if (act_dtype == B200_BF16 && w_dtype == B200_BF16) { CALL(__nv_bfloat16, __nv_bfloat16); }
   else if (act_dtype == B200_BF16 && w_dtype == B200_F32) { CALL(__nv_bfloat16, float); }

@@ -205,12 +205,16 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Ten
     wcode = _code(q_weight) if q_weight is not None else _code(qkv)
     if q_weight is not None and k_weight.dtype != q_weight.dtype:
         raise KernelError("q and k norm weights must share a dtype")
-    cache_slots = 0 if k_cache is None else k_cache.shape[0] * k_cache.shape[1]
+    # cache tensors are [pages + 1, kv_heads, page_size, head_dim]
+    page_size = 1 if k_cache is None else k_cache.shape[2]
+    cache_slots = 0 if k_cache is None else k_cache.shape[0] * k_cache.shape[2]
+    if k_cache is not None and (k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim):
+        raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
     max_pos = 0 if cos is None else cos.shape[0]
     lib = load_cuda_library("qkv_post.cu")
     rc = lib.b200_qkv_post(_p(qkv), _p(q_out), _p(k_cache), _p(v_cache), _p(q_weight), _p(k_weight),
                            ctypes.c_float(eps), _p(cos), _p(sin), rot_dim, max_pos, _p(positions), _p(slots),
-                           tokens, num_heads, num_kv_heads, head_dim, ctypes.c_longlong(cache_slots),
+                           tokens, num_heads, num_kv_heads, head_dim, page_size, ctypes.c_longlong(cache_slots),
                            _code(qkv), wcode, _p(error_word(qkv.device)), _stream())
     _ok(rc, "qkv_post")
 
@@ -240,16 +244,40 @@ def _attention_mma(head_dim: int):
     return load_cuda_library("attention_mma.cu", {"HEAD_DIM": head_dim})
 
 
-def decode_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
-    """bfloat16 caches with at most 16 query heads per KV head and heads up to 256 wide take the
-    tensor-core kernel; everything else (float32, wider groups or heads) the all-sizes kernel."""
+def decode_uses_tensor_cores(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
+                             page_size: int) -> bool:
+    """bfloat16 caches with at most 16 query heads per KV head, heads up to 256 wide and a page size
+    that is a power of two take the TMA / tensor-core kernel; everything else the all-sizes kernel."""
     return (dtype == torch.bfloat16 and num_heads // num_kv_heads <= MMA_MAX_GROUP
-            and head_dim <= MMA_MAX_HEAD_DIM and head_dim % 16 == 0)
+            and head_dim <= MMA_MAX_HEAD_DIM and head_dim % 16 == 0
+            and page_size > 0 and page_size & (page_size - 1) == 0)
 
 
-def decode_ctas_per_split(dtype: torch.dtype, n_rows: int, num_heads: int, num_kv_heads: int, head_dim: int) -> int:
+_kv_maps = {}
+
+
+def kv_tensor_map(cache: torch.Tensor, box_rows: int):
+    """The 128-byte TMA descriptor of a cache tensor [pages + 1, kv_heads, page_size, head_dim] (made once)."""
+    key = (cache.data_ptr(), tuple(cache.shape), box_rows)
+    buf = _kv_maps.get(key)
+    if buf is None:
+        if cache.dtype != torch.bfloat16 or not cache.is_contiguous() or cache.dim() != 4:
+            raise KernelError("a TMA descriptor needs a contiguous bfloat16 cache [pages + 1, kv_heads, page_size, head_dim]")
+        buf = ctypes.create_string_buffer(128)
+        rows = cache.shape[0] * cache.shape[1] * cache.shape[2]
+        rc = _attention_mma(cache.shape[3]).b200_kv_tensor_map(buf, _p(cache), ctypes.c_longlong(rows), box_rows)
+        if rc != 0:
+            raise KernelError(f"the TMA descriptor of a cache tensor could not be made (code {rc})")
+        if len(_kv_maps) > 4096:
+            _kv_maps.clear()
+        _kv_maps[key] = buf
+    return buf
+
+
+def decode_ctas_per_split(dtype: torch.dtype, n_rows: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                          page_size: int) -> int:
     """CTAs that the decode kernel launches for each split of the keys."""
-    if decode_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim):
+    if decode_uses_tensor_cores(dtype, num_heads, num_kv_heads, head_dim, page_size):
         return n_rows * num_kv_heads
     return n_rows * num_kv_heads * ((num_heads // num_kv_heads + 3) // 4)
 
@@ -270,9 +298,12 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     need = decode_scratch_floats(n_rows, num_heads, head_dim, splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"decode attention needs {need} floats of scratch")
-    if decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim):
+    if decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
+            raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
+        box_rows = min(page_size, 32)
         rc = _attention_mma(head_dim).b200_decode_attention_mma(
-            _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
+            _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
             _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
             ctypes.c_float(scale), splits, _p(error_word(q.device)), _stream())
         _ok(rc, "decode_attention_mma", 2 if splits > 1 else 1)

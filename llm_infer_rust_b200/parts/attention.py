@@ -94,7 +94,7 @@ class GQAttention(Part):
                                   self.nh, self.nkv, self.d, page, self.window, self.scale)
         if ctx.num_decode:
             bound = min(ctx.kv_len_bound, self.window) if self.window else ctx.kv_len_bound
-            per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, self.nh, self.nkv, self.d)
+            per_split = ops.decode_ctas_per_split(q.dtype, ctx.num_decode, self.nh, self.nkv, self.d, page)
             splits = decode_splits(per_split, bound, ctx.sm_count)
             need = ops.decode_scratch_floats(ctx.num_decode, self.nh, self.d, splits)
             scratch = ctx.scratch(need) if need else None

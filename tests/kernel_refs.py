@@ -63,12 +63,13 @@ def ref_qkv_post(qkv, q_w, k_w, eps, cos, sin, rot_dim, positions, nh, nkv, d):
 
 
 def ref_store_kv(k_cache, v_cache, k, v, slots):
-    """cache[slot] = row for every token; slot 0 (the sink) is skipped."""
-    flat_k = k_cache.view(-1, k_cache.shape[-2], k_cache.shape[-1])
-    flat_v = v_cache.view(-1, v_cache.shape[-2], v_cache.shape[-1])
+    """cache[page, :, offset] = row for every token (slot = page * page_size + offset); slot 0 (the
+    sink) is skipped.  Caches are [pages + 1, kv_heads, page_size, head_dim]."""
+    page_size = k_cache.shape[2]
     keep = slots != 0
-    flat_k[slots[keep].long()] = k[keep]
-    flat_v[slots[keep].long()] = v[keep]
+    page, off = (slots[keep] // page_size).long(), (slots[keep] % page_size).long()
+    k_cache[page, :, off] = k[keep]
+    v_cache[page, :, off] = v[keep]
 
 
 def ref_paged_attention(q, k_cache, v_cache, block_table, cu_q, kv_len, prefix_len, nh, nkv, d,
@@ -80,8 +81,9 @@ def ref_paged_attention(q, k_cache, v_cache, block_table, cu_q, kv_len, prefix_l
     out = torch.zeros_like(q)
     qv = q.float().view(-1, nh, d)
     ov = out.view(-1, nh, d)
-    flat_k = k_cache.float().view(-1, nkv, d)
-    flat_v = v_cache.float().view(-1, nkv, d)
+    # [pages + 1, kv_heads, page_size, d] -> one row of all KV heads per slot
+    flat_k = k_cache.float().permute(0, 2, 1, 3).reshape(-1, nkv, d)
+    flat_v = v_cache.float().permute(0, 2, 1, 3).reshape(-1, nkv, d)
     g = nh // nkv
     n_rows = cu_q.numel() - 1
     for r in (range(n_rows) if rows is None else [int(x) for x in rows]):

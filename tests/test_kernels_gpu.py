@@ -147,8 +147,8 @@ def test_qkv_post(dtype, nh, nkv, d, rot, eps, with_norm):
     slots = (torch.randperm(page * pages, generator=g)[:tokens] + page).to(torch.int32)
     slots[3] = 0                                              # a padding row: writes nothing
     slots = slots.to(DEV)
-    kc = torch.full((pages + 1, page, nkv, d), 7.0, dtype=dtype, device=DEV)
-    vc = torch.full((pages + 1, page, nkv, d), 7.0, dtype=dtype, device=DEV)
+    kc = torch.full((pages + 1, nkv, page, d), 7.0, dtype=dtype, device=DEV)
+    vc = torch.full((pages + 1, nkv, page, d), 7.0, dtype=dtype, device=DEV)
     q = torch.empty(tokens, nh * d, dtype=dtype, device=DEV)
     o.qkv_post(qkv, q, kc, vc, qw, kw, eps, cos, sin, rot, positions, slots, nh, nkv, d)
     rq, rk, rv = R.ref_qkv_post(qkv, qw, kw, eps, cos, sin, rot, positions, nh, nkv, d)
@@ -169,7 +169,7 @@ def test_qkv_post_flags_bad_positions_and_slots():
     o = ops()
     qkv = rnd(2, 3 * 16)
     cos = torch.ones(4, 8, device=DEV)
-    kc = torch.zeros(3, 2, 1, 16, device=DEV)
+    kc = torch.zeros(3, 1, 2, 16, device=DEV)
     q = torch.empty(2, 16, device=DEV)
     pos = torch.tensor([0, 4], dtype=torch.int32, device=DEV)
     slots = torch.tensor([2, 3], dtype=torch.int32, device=DEV)
@@ -192,8 +192,8 @@ def paged_case(rows, nh, nkv, d, page, dtype, seed=0, poison=True):
     perm = (torch.randperm(total_pages, generator=g) + 1).tolist()
     width = max(need) + 1
     table = torch.zeros(len(rows), width, dtype=torch.int32)
-    kc = torch.full((total_pages + 1, page, nkv, d), 1e4 if poison else 0.0)
-    vc = torch.full((total_pages + 1, page, nkv, d), -1e4 if poison else 0.0)
+    kc = torch.full((total_pages + 1, nkv, page, d), 1e4 if poison else 0.0)
+    vc = torch.full((total_pages + 1, nkv, page, d), -1e4 if poison else 0.0)
     at = 0
     for r, (p, n) in enumerate(rows):
         for lp in range(need[r]):
@@ -201,8 +201,8 @@ def paged_case(rows, nh, nkv, d, page, dtype, seed=0, poison=True):
             at += 1
         for pos in range(p + n):
             slot_page, off = table[r, pos // page], pos % page
-            kc[slot_page, off] = torch.randn(nkv, d, generator=g)
-            vc[slot_page, off] = torch.randn(nkv, d, generator=g)
+            kc[slot_page, :, off] = torch.randn(nkv, d, generator=g)
+            vc[slot_page, :, off] = torch.randn(nkv, d, generator=g)
     tq = sum(n for _, n in rows)
     q = torch.randn(tq, nh * d, generator=g)
     cu = torch.tensor([0] + list(torch.tensor([n for _, n in rows]).cumsum(0)), dtype=torch.int32)
@@ -264,9 +264,9 @@ def test_attention_finds_one_far_key_among_a_thousand():
         c = paged_case([(999, 1), (990, 10)], nh, nkv, d, page, torch.float32, seed=far, poison=False)
         for r in range(2):
             pg, off = c["table"][r, far // page], far % page
-            c["kc"][pg, off] = 0.0
-            c["kc"][pg, off, :, 0] = 50.0
-            c["vc"][pg, off] = 3.0
+            c["kc"][pg, :, off] = 0.0
+            c["kc"][pg, :, off, 0] = 50.0
+            c["vc"][pg, :, off] = 3.0
         c["q"][:, 0::d] = 1.0                                  # dimension 0 of every head
         scale = 1.0
         out = torch.empty_like(c["q"])
@@ -296,8 +296,8 @@ def test_window_edge_is_exact():
         p = 40
         key = p - W + 1 if inside else p - W
         for r in range(2):
-            c["kc"][c["table"][r, key // page], key % page, 0, 0] = 60.0
-            c["vc"][c["table"][r, key // page], key % page] = 5.0
+            c["kc"][c["table"][r, key // page], 0, key % page, 0] = 60.0
+            c["vc"][c["table"][r, key // page], :, key % page] = 5.0
         out = torch.empty_like(c["q"])
         o.decode_attention(c["q"], c["kc"], c["vc"], out, None, c["table"], c["cu"], c["kv_len"],
                            torch.tensor([0], dtype=torch.int32, device=DEV), 1, nh, nkv, d, page, W, 1.0, 1)

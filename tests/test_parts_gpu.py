@@ -148,7 +148,7 @@ def test_attention_part_over_its_cache(nh, nkv, d, window, qk_eps):
 
     want = {r: plain(x) for r, x in xs.items()}
     mgr = rt.CacheManager([rt.GroupSpec(page, 30, window or 0)], 4)
-    cache = LayerCache(group=0, k=torch.zeros(31, page, nkv, d, device=DEV), v=torch.zeros(31, page, nkv, d, device=DEV))
+    cache = LayerCache(group=0, k=torch.zeros(31, nkv, page, d, device=DEV), v=torch.zeros(31, nkv, page, d, device=DEV))
     mgr.open(1)
     mgr.open(2)
     got = {1: [], 2: []}

@@ -30,8 +30,8 @@ def _case(n_rows, nh, nkv, d, page, ctx, dtype, seed):
     total = n_rows * pages_per_row
     perm = torch.randperm(total, generator=g) + 1
     table = perm.view(n_rows, pages_per_row).to(torch.int32)
-    kc = torch.randn(total + 1, page, nkv, d, generator=g).to(dtype)
-    vc = torch.randn(total + 1, page, nkv, d, generator=g).to(dtype)
+    kc = torch.randn(total + 1, nkv, page, d, generator=g).to(dtype)
+    vc = torch.randn(total + 1, nkv, page, d, generator=g).to(dtype)
     q = torch.randn(n_rows, nh * d, generator=g).to(dtype)
     kv_len = torch.tensor([ctx - 3 * r for r in range(n_rows)], dtype=torch.int32)
     cu = torch.arange(n_rows + 1, dtype=torch.int32)
