@@ -381,6 +381,147 @@ __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __r
   }
 }
 
+// ------------------------------------------------------------------ prompt portions
+// grid (query tiles, nkv, prefill rows).  A CTA serves PF_WARPS * 16 query vectors: consecutive
+// tokens of one row x the `group` query heads of one KV head; warp w owns vectors 16 w .. 16 w + 15
+// (a warp holds 16 / group whole tokens).  All warps read the same key blocks, which one warp fetches
+// into a ring of stages: full[s] flips when the boxes of a block have landed, empty[s] when every
+// warp has finished with it.  Each query vector has its own position, so the causal mask (and the
+// window) is applied per row of the score tile.
+constexpr int PF_WARPS = 4;
+constexpr int PF_ROWS = PF_WARPS * 16;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(PF_WARPS * 32, 1)
+prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                   const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
+                   int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                   const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv, int page_size,
+                   int box_rows, int window, float scale_log2, int* err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  bf16* qs = reinterpret_cast<bf16*>(tiles + static_cast<size_t>(STAGES) * TILE_BYTES);     // [PF_ROWS][LD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(qs + PF_ROWS * LD);
+  uint64_t* empty = full + STAGES;
+
+  const int row = rows[blockIdx.z];
+  const int kvh = blockIdx.y;
+  const int group = nh / nkv, head0 = kvh * group;
+  const int tokens_per_warp = 16 / group;                       // whole tokens per warp
+  const int tile_tokens = tokens_per_warp * PF_WARPS;
+  const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
+  const int tok0 = blockIdx.x * tile_tokens;
+  if (tok0 >= q_len) return;
+  const int ntok = min(tile_tokens, q_len - tok0);
+  const int prefix = prefix_len[row];
+  const int kv_end = min(kv_len[row], prefix + tok0 + ntok);     // causal: nothing later is visible to this tile
+  const int p_lo = prefix + tok0;
+  int k_begin = window > 0 ? max(0, p_lo - window + 1) : 0;
+  k_begin -= k_begin % KB;
+  const int nblk = (kv_end - k_begin + KB - 1) / KB;
+  const int* table = block_table + static_cast<size_t>(row) * table_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  for (int c = threadIdx.x; c < PF_ROWS * (D / 8); c += blockDim.x) {
+    const int r = c / (D / 8), part = c - r * (D / 8);
+    const int w = r >> 4, i = r & 15;
+    const int tok = w * tokens_per_warp + i / group, head = head0 + i % group;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (i < tokens_per_warp * group && tok < ntok)
+      v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D + part * 8);
+    *reinterpret_cast<uint4*>(qs + r * LD + part * 8) = v;
+  }
+  if (threadIdx.x < STAGES) { mbar_init(full + threadIdx.x, 1); mbar_init(empty + threadIdx.x, PF_WARPS); }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  __syncthreads();
+
+  // Positions of this thread's two score rows (lane / 4 and lane / 4 + 8 of the warp's 16 vectors).
+  const int g = lane >> 2;
+  int qpos[2], tok_of[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int i = g + 8 * h;
+    const int tok = warp * tokens_per_warp + i / group;
+    const bool used = i < tokens_per_warp * group && tok < ntok;
+    tok_of[h] = used ? tok : -1;
+    qpos[h] = used ? p_lo + tok : -1;
+  }
+  // The warp's own range of key blocks: from its first visible key to its last query's position.
+  const int w_tok_lo = warp * tokens_per_warp;
+  const int w_tok_hi = min(ntok, w_tok_lo + tokens_per_warp) - 1;           // < w_tok_lo: the warp holds no token
+  const int w_p_hi = p_lo + w_tok_hi;
+  const int w_first_key = window > 0 ? max(0, p_lo + w_tok_lo - window + 1) : 0;
+
+  WarpAcc st;
+  st.init();
+  const bf16* my_q = qs + warp * 16 * LD;
+  bool ok = true;
+  int page = 0;
+  if (warp == 0) {                                                          // prologue of the producer
+    page = nblk > 0 ? lane_page(table, page_size, box_rows, k_begin, kv_end, lane) : 0;
+    for (int j = 0; j < STAGES - 1 && j < nblk; ++j) {
+      const int next_page = j + 1 < nblk ? lane_page(table, page_size, box_rows, k_begin + (j + 1) * KB, kv_end, lane) : 0;
+      fetch_block(tiles + j * TILE_BYTES, &kmap, &vmap, page, page_size, nkv, kvh, box_rows, k_begin + j * KB, kv_end,
+                  full + j, lane);
+      page = next_page;
+    }
+  }
+  for (int it = 0; it < nblk && ok; ++it) {
+    const int s = it % STAGES;
+    if (warp == 0) {
+      const int j = it + STAGES - 1;
+      if (j < nblk) {
+        const int sj = j % STAGES, use = j / STAGES;
+        const int next_page = j + 1 < nblk ? lane_page(table, page_size, box_rows, k_begin + (j + 1) * KB, kv_end, lane) : 0;
+        if (use > 0) ok = mbar_wait(empty + sj, (use - 1) & 1, err);          // every warp has left block j - STAGES
+        if (ok)
+          fetch_block(tiles + sj * TILE_BYTES, &kmap, &vmap, page, page_size, nkv, kvh, box_rows, k_begin + j * KB,
+                      kv_end, full + sj, lane);
+        page = next_page;
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) break;
+    if (!mbar_wait(full + s, (it / STAGES) & 1, err)) { ok = false; break; }
+    unsigned char* t = tiles + s * TILE_BYTES;
+    const int first_key = k_begin + it * KB;
+    if (first_key + KB > kv_end && first_key + lane >= kv_end) {
+      // Value rows beyond what this tile may see hold whatever the page or the stage held before (they are
+      // masked for every query of the tile): keep them out of P.V.
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
+    }
+    __syncwarp();
+    if (w_tok_hi >= w_tok_lo && first_key <= w_p_hi && first_key + KB > w_first_key)
+      block_mma(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], scale_log2, st);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + s);
+  }
+  if (!ok) {
+    // A wait ran out: let the copies in flight land (bounded) before the CTA gives up its shared memory.
+    for (int s = 0; s < STAGES; ++s) { mbar_wait(full + s, 0, err); }
+    return;
+  }
+  st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 1); st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], 2);
+  st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 1); st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], 2);
+  const int t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (tok_of[h] < 0) continue;
+    const int head = head0 + (g + 8 * h) % group;
+    bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok_of[h]) * nh + head) * D;
+    const float inv = st.l[h] > 0.0f ? 1.0f / st.l[h] : 0.0f;
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn)
+      *reinterpret_cast<uint32_t*>(dst + dn * 8 + t2) = pack_bf16(st.o[dn][2 * h] * inv, st.o[dn][2 * h + 1] * inv);
+  }
+}
+
 // ------------------------------------------------------------------ launchers
 constexpr size_t kSmemLimit = 226 * 1024;
 constexpr size_t kQBytes = QROWS * LD * sizeof(bf16);
@@ -463,5 +604,40 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   dim3 mgrid(n_rows, nh);
   decode_mma_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(static_cast<bf16*>(out), part_acc, part_ml, cu_q,
                                                                     rows, nh, splits);
+  return b200_check_launch();
+}
+
+constexpr size_t kPfQBytes = PF_ROWS * LD * sizeof(bf16);
+constexpr size_t kPfFixed = 1024 + kPfQBytes + kBarBytes;
+constexpr int kPfStages = kPfFixed + 4 * TILE_BYTES <= kSmemLimit ? 4 : (kPfFixed + 3 * TILE_BYTES <= kSmemLimit ? 3 : 2);
+static_assert(kPfFixed + kPfStages * TILE_BYTES <= kSmemLimit, "the key blocks must fit shared memory");
+
+// Portions of prompts over a bfloat16 cache; arguments as b200_prefill_attention of attention.cu, with the
+// descriptors of b200_kv_tensor_map in place of the cache pointers.
+B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, const void* v_map, void* out,
+                                           const int* block_table, int table_stride, const int* cu_q,
+                                           const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
+                                           int max_q_len, int nh, int nkv, int page_size, int window, float scale,
+                                           int* err, cudaStream_t stream) {
+  if (n_rows <= 0 || max_q_len <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh / nkv > QROWS || page_size <= 0) return B200_BAD_SIZE;
+  if ((page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
+  const int box_rows = page_size < KB ? page_size : KB;
+  const int tile_tokens = (16 / (nh / nkv)) * PF_WARPS;
+  constexpr size_t smem = kPfFixed + static_cast<size_t>(kPfStages) * TILE_BYTES;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<kPfStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  CUtensorMap kmap, vmap;
+  memcpy(&kmap, k_map, sizeof(kmap));
+  memcpy(&vmap, v_map, sizeof(vmap));
+  dim3 grid((max_q_len + tile_tokens - 1) / tile_tokens, nkv, n_rows);
+  prefill_mma_kernel<kPfStages><<<grid, PF_WARPS * 32, smem, stream>>>(
+      kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
+      prefix_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
   return b200_check_launch();
 }

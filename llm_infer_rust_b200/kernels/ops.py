@@ -229,6 +229,16 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
         return
     if k_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("q, cache and output must share a dtype")
+    if decode_uses_tensor_cores(q.dtype, num_heads, num_kv_heads, head_dim, page_size):
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
+            raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
+        box_rows = min(page_size, 32)
+        rc = _attention_mma(head_dim).b200_prefill_attention_mma(
+            _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
+            block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
+            num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), _p(error_word(q.device)), _stream())
+        _ok(rc, "prefill_attention_mma")
+        return
     rc = _attention(head_dim).b200_prefill_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
         _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,

@@ -21,10 +21,17 @@ def ops():
     return o
 
 
-def close(got, want, dtype, atol=1e-5, rtol=1e-5):
+def close(got, want, dtype, atol=1e-5, rtol=1e-5, bf16_atol=2e-3):
     if dtype == torch.bfloat16:
-        atol, rtol = 2e-3, BF16_RTOL
+        atol, rtol = bf16_atol, BF16_RTOL
     torch.testing.assert_close(got.float(), want.float(), atol=atol, rtol=rtol)
+
+
+def attention_atol(case):
+    """Bound of the bfloat16 attention kernels' error: the tensor-core kernels round every probability
+    to bfloat16 (2^-9 relative) as the operand of P.V, so an output is off by at most 2^-9 * sum p |v|
+    <= 2^-9 * max |v|, and once more by its own rounding to bfloat16: 2^-8 * max |v| in all."""
+    return 2.0 ** -8 * case["vmax"]
 
 
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
@@ -203,6 +210,7 @@ def paged_case(rows, nh, nkv, d, page, dtype, seed=0, poison=True):
             slot_page, off = table[r, pos // page], pos % page
             kc[slot_page, :, off] = torch.randn(nkv, d, generator=g)
             vc[slot_page, :, off] = torch.randn(nkv, d, generator=g)
+    vmax = float(vc[vc > -1e3].abs().max()) if poison else float(vc.abs().max())
     tq = sum(n for _, n in rows)
     q = torch.randn(tq, nh * d, generator=g)
     cu = torch.tensor([0] + list(torch.tensor([n for _, n in rows]).cumsum(0)), dtype=torch.int32)
@@ -210,7 +218,7 @@ def paged_case(rows, nh, nkv, d, page, dtype, seed=0, poison=True):
     prefix = torch.tensor([p for p, _ in rows], dtype=torch.int32)
     dev = lambda t: t.to(DEV)
     return dict(q=dev(q.to(dtype)), kc=dev(kc.to(dtype)), vc=dev(vc.to(dtype)), table=dev(table), cu=dev(cu),
-                kv_len=dev(kv_len), prefix=dev(prefix))
+                kv_len=dev(kv_len), prefix=dev(prefix), vmax=vmax)
 
 
 ATT_CASES = [  # nh, nkv, d, page, window
@@ -232,7 +240,7 @@ def test_prefill_attention(dtype, nh, nkv, d, page, window):
                         64, nh, nkv, d, page, window, scale)
     want = R.ref_paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["kv_len"], c["prefix"], nh, nkv,
                                  d, page, window, scale, rows=[1, 2, 3, 4])
-    close(out[1:], want[1:], dtype, atol=2e-5, rtol=1e-4)
+    close(out[1:], want[1:], dtype, atol=2e-5, rtol=1e-4, bf16_atol=attention_atol(c))
     assert (out[0] == 9.0).all()                              # a row that was not listed is not touched
 
 
@@ -252,7 +260,7 @@ def test_decode_attention(dtype, nh, nkv, d, page, window, splits):
                        d, page, window, scale, splits)
     want = R.ref_paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["kv_len"], c["prefix"], nh, nkv,
                                  d, page, window, scale, rows=range(6))
-    close(out[:6], want[:6], dtype, atol=2e-5, rtol=1e-4)
+    close(out[:6], want[:6], dtype, atol=2e-5, rtol=1e-4, bf16_atol=attention_atol(c))
     assert (out[6:] == 9.0).all()
 
 
