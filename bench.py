@@ -251,7 +251,8 @@ def main() -> int:
     pool_tokens = biggest * (args.context + 128) + 4096
     engine = Engine(None, random_weights_config=raw, random_weights_seed=0, dtype="bfloat16",
                     max_running_req=biggest, max_seq_len=args.context + 64, page_size=16,
-                    max_total_tokens=pool_tokens, cuda_graph_bs=biggest, chunked_prefill_size=4096)
+                    max_total_tokens=pool_tokens, cuda_graph_bs=biggest, chunked_prefill_size=4096,
+                    prefill_cuda_graph_max_tokens=2048)
 
     if args.only == "decode":
         run = decode_device_timed(engine, args.batch, args.context, args.steps, args.warmup, vocab)
@@ -287,7 +288,7 @@ def main() -> int:
                    "intermediate": raw["intermediate_size"], "vocab": vocab, "tied": raw["tie_word_embeddings"],
                    "global_batch": args.batch, "seq_len": args.context,
                    "prompt_len": args.context - args.steps - args.warmup, "page_size": 16,
-                   "parallelism": "single GPU", "decode_graphs": True,
+                   "parallelism": "single GPU", "decode_graphs": True, "prefill_graph": True,
                    "l2": "inputs exceed L2: every step reads all weights and the live cache",
                    "peaks": peak_source},
         "clocks": clock_record,

@@ -22,6 +22,8 @@ Options (as in the reference where it has them):
   --max-prefill-tokens-per-batch N  Maximum uncached prefill tokens per batch (0 disables; default 8192)
   --chunked-prefill-size N  Prefill token budget with long-request chunking (-1/0 disables; omitted auto-selects)
   --cuda-graph-bs N         Maximum CUDA decode graph batch (0 disables; default max-running-req)
+  --prefill-cuda-graph-max-tokens N  Largest step with prompt tokens that is captured as a CUDA graph when its
+                            shape repeats (0 disables; default 2048)
   --max-seq-len N           Maximum sequence length (default 8192, at most the model's; must not exceed model config)
   --page-size N             KV cache page size (default 16)
   --dtype NAME              Model dtype: auto, bfloat16, float32
@@ -48,6 +50,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-prefill-tokens-per-batch", type=int, default=8192)
     p.add_argument("--chunked-prefill-size", type=int, default=None)
     p.add_argument("--cuda-graph-bs", type=int, default=None)
+    p.add_argument("--prefill-cuda-graph-max-tokens", type=int, default=2048)
     p.add_argument("--max-seq-len", type=int, default=None)
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--dtype", default="auto", choices=["auto", "bfloat16", "float32"])
@@ -109,6 +112,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                     max_total_tokens=args.max_total_tokens,
                     max_prefill_tokens_per_batch=args.max_prefill_tokens_per_batch,
                     chunked_prefill_size=args.chunked_prefill_size, cuda_graph_bs=args.cuda_graph_bs,
+                    prefill_cuda_graph_max_tokens=args.prefill_cuda_graph_max_tokens,
                     seed=args.seed, log_level=args.log_level)
     params = SamplingParams(args.temperature, args.top_k, args.top_p, args.ignore_eos, args.max_tokens,
                             args.seed if args.seed else None)

@@ -14,6 +14,7 @@ all go through it.
 from __future__ import annotations
 
 import os
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -125,7 +126,8 @@ class Engine:
                  max_running_req: int = 256, max_seq_len: Optional[int] = None, page_size: int = 16,
                  memory_ratio: float = 0.9, max_total_tokens: Optional[int] = None,
                  max_prefill_tokens_per_batch: int = 8192, chunked_prefill_size: Optional[int] = None,
-                 cuda_graph_bs: Optional[int] = 0, eos_token_ids: Optional[Sequence[int]] = None,
+                 cuda_graph_bs: Optional[int] = 0, prefill_cuda_graph_max_tokens: int = 0,
+                 eos_token_ids: Optional[Sequence[int]] = None,
                  seed: int = 0, log_level: str = "info", random_weights_config: Optional[dict] = None,
                  random_weights_seed: int = 0):
         """``model_path``: a folder with config.json and model.safetensors.  With ``model_path`` None and
@@ -211,6 +213,14 @@ class Engine:
         self.cuda_graph_bs = min(int(cuda_graph_bs), max_running_req) if self.dtype == torch.bfloat16 else 0
         for bucket in graph_batch_sizes(self.cuda_graph_bs):
             self._graphs[bucket] = _DecodeGraph(bucket)
+        # Graphs of steps that hold prompt portions, keyed by the exact shape of the batch (the rows'
+        # token counts and the number of wanted logits).  A shape is captured when it comes a second
+        # time (a long prompt cut into equal portions, a server's usual chunk) and replayed from then
+        # on; the least recently used graph goes when there are more than a handful.
+        self.prefill_graph_max_tokens = int(prefill_cuda_graph_max_tokens) if self.dtype == torch.bfloat16 else 0
+        self._shape_graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
+        self._shape_seen: Dict[tuple, int] = {}
+        self._shape_graph_limit = 6
 
     # ------------------------------------------------------------------ the device
     def _setup_device(self, device: str) -> None:
@@ -298,6 +308,9 @@ class Engine:
             bucket = next((b for b in sorted(self._graphs) if b >= len(entries)), None)
             if bucket is not None and max(mgr.length(e.request) for e in entries) < self.max_seq_len:
                 graph = self._graphs[bucket]
+        if graph is None and not decode_only and 0 < len(req.tokens) <= self.prefill_graph_max_tokens \
+                and max(mgr.length(e.request) + len(e.tokens) for e in entries) <= self.max_seq_len:
+            graph = self._shape_graph(tuple(req.counts) + (-1, len(req.want_index)))
         if graph is not None:
             logits = self._step_graph(graph, req, len(entries), device_tokens)
         else:
@@ -316,6 +329,23 @@ class Engine:
             dev[layout.off_tokens:layout.off_tokens + layout.num_tokens].copy_(device_tokens, non_blocking=True)
         ctx = self._context(layout, dev, host, layout.max_kv_len)
         return self.model.forward(ctx, self.cache.layer_caches)
+
+    def _shape_graph(self, key: tuple) -> Optional[_DecodeGraph]:
+        g = self._shape_graphs.get(key)
+        if g is not None:
+            self._shape_graphs.move_to_end(key)
+            return g
+        seen = self._shape_seen.get(key, 0) + 1
+        if len(self._shape_seen) > 4096:
+            self._shape_seen.clear()
+        self._shape_seen[key] = seen
+        if seen < 2:
+            return None                      # a shape that comes once is not worth a capture
+        g = _DecodeGraph(0)
+        self._shape_graphs[key] = g
+        while len(self._shape_graphs) > self._shape_graph_limit:
+            self._shape_graphs.popitem(last=False)
+        return g
 
     def _step_graph(self, g: _DecodeGraph, req, real_rows: int,
                     device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -350,7 +380,7 @@ class Engine:
             g.meta[layout.off_tokens:layout.off_tokens + real_rows].copy_(device_tokens, non_blocking=True)
         g.graph.replay()
         ops.add_launches(g.launches)
-        return g.logits[:real_rows]
+        return g.logits[:real_rows] if g.bucket else g.logits
 
     def capture_graphs(self) -> None:
         """Capture every decode graph bucket now (else each is captured at its first use)."""

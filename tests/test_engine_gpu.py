@@ -189,6 +189,31 @@ def test_decode_graphs_give_the_eager_logits(tiny, tiny_dirs, tmp_path):
     assert [len(r.tokens) for r in res] == [16, 16, 16] and graph.cache.manager.live_requests() == 0
 
 
+def test_graphs_of_repeated_prompt_portions_give_the_eager_logits(tiny, tmp_path):
+    from llm_infer_rust_b200 import write_random_model
+    from llm_infer_rust_b200.engine import StepEntry
+    v = tiny["C"]
+    folder = write_random_model(str(tmp_path / "m"), v["raw"], v["seed"], norm_std=v["norm_std"], dtype="bfloat16")
+    eager = engine(folder, dtype="bfloat16", page_size=8, max_total_tokens=1024)
+    graph = engine(folder, dtype="bfloat16", page_size=8, max_total_tokens=1024, prefill_cuda_graph_max_tokens=64)
+    prompts = {1: tokens(301, 96, 1), 2: tokens(301, 112, 2)}
+    for eng in (eager, graph):
+        eng.open_request(1)
+        eng.open_request(2)
+    # portions of 16 alone, then 16 beside a decoded token of the other request, then an odd tail
+    plan = [[(1, 16)]] * 4 + [[(2, 16)]] * 3 + [[(1, 16), (2, 1)]] * 2 + [[(2, 31)], [(2, 31)]]
+    fed = {1: 0, 2: 0}
+    for step, rows in enumerate(plan):
+        entries = [StepEntry(r, prompts[r][fed[r]: fed[r] + n], [n - 1, 0]) for r, n in rows]
+        for r, n in rows:
+            fed[r] += n
+        a = eager.step(entries).clone()
+        b = graph.step(entries).clone()
+        assert (a - b).abs().max() <= 2.0 ** -6 * max(1.0, float(a.abs().max())), step
+    assert len(graph._shape_graphs) == 3 and all(g.graph is not None for g in graph._shape_graphs.values())
+    graph.check_kernel_errors()
+
+
 def test_command_line(tiny, tiny_dirs, tmp_path):
     from llm_infer_rust_b200 import SamplingParams
     want = engine(tiny_dirs["A"], dtype="float32", page_size=4, max_total_tokens=256).generate(
