@@ -17,9 +17,12 @@
 // The joint cut-off needs no sort: "keep p >= t" with
 //   t = max{ t : count(p >= t) >= k  or  mass(p >= t) >= top_p }
 // is found by bisection over the bit patterns of positive floats.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 struct SampleRow {          // 32 bytes, filled by the host
   float temperature;
@@ -55,9 +58,9 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
   return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;      // ties: the lowest index
 }
 
-__device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx* sh) {
+__device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx* sh, int begin = 0) {
   MaxIdx best = {-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  for (int i = begin + threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = row[i];
     if (!(v != v)) best = better(best, MaxIdx{v, i});             // NaN never wins
   }
@@ -80,6 +83,31 @@ __device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx*
   }
   __syncthreads();
   return sh[32];
+}
+
+// A large vocabulary is shared by a cluster of ARGMAX_CLUSTER CTAs per row: every CTA scans one slice, sends
+// its best (value, index) to the first CTA of the cluster through distributed shared memory, and that one
+// picks the winner (ties: the lowest index, as in the one-CTA kernel).
+constexpr int ARGMAX_CLUSTER = 8;
+
+__global__ void __launch_bounds__(THREADS)
+argmax_cluster_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int* __restrict__ out, int* err) {
+  __shared__ MaxIdx sh[33];
+  __shared__ MaxIdx partial[ARGMAX_CLUSTER];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int row = blockIdx.x / ARGMAX_CLUSTER;
+  const int slice = (vocab + ARGMAX_CLUSTER - 1) / ARGMAX_CLUSTER;
+  const int begin = min(vocab, rank * slice), end = min(vocab, begin + slice);
+  const MaxIdx b = block_argmax(logits + row * row_stride, end, sh, begin);
+  if (threadIdx.x == 0) *cluster.map_shared_rank(&partial[rank], 0) = b;
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    MaxIdx best = partial[0];
+    for (int r = 1; r < ARGMAX_CLUSTER; ++r) best = better(best, partial[r]);
+    if (best.i >= vocab) { atomicOr(err, B200_ERR_SAMPLING); out[row] = -1; }
+    else out[row] = best.i;
+  }
 }
 
 __global__ void __launch_bounds__(THREADS)
@@ -204,6 +232,21 @@ B200_EXPORT int b200_argmax(const float* logits, long long row_stride, int rows,
                             cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return B200_BAD_SIZE;
+  if (vocab >= 16384 && rows <= 4096) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(rows * ARGMAX_CLUSTER);
+    config.blockDim = dim3(THREADS);
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ARGMAX_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, argmax_cluster_kernel, logits, row_stride, vocab, out, err);
+    return e == cudaSuccess ? b200_check_launch() : static_cast<int>(e);
+  }
   argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, vocab, out, err);
   return b200_check_launch();
 }

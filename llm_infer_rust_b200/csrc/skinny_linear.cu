@@ -1,0 +1,477 @@
+// y = epilogue(prologue(x) . W^T) for a handful of rows (decode steps): the weights are streamed once,
+// at the speed of memory, and what stands before and after the product is fused into the same kernel.
+//
+//   prologue  none, or residual add + RMSNorm: s = x + residual in float, residual_out = round(s),
+//             x' = s * rsqrt(mean(s^2) + eps) * w (the unrounded sum is normalised; reference:
+//             src/layers/fused_ops.cu:95-105).  Every CTA recomputes the row statistics (the rows are few
+//             and sit in L2); the CTA with index 0 writes residual_out.
+//   product   W is [N, K] bfloat16, row-major.  A CTA owns BN = 64 * MT weight rows and a range of K; TMA
+//             brings boxes of BN rows x 64 columns (128-byte swizzle) into a ring of stages, the rows of
+//             x' (at most 16) wait in shared memory, and mma.sync m16n8k16 multiplies with the WEIGHT rows
+//             on the 16-row side of the instruction, so no tensor work is wasted on padding the rows.
+//             Where N / BN alone would leave SMs idle, a thread-block cluster of up to 8 CTAs splits K; the
+//             partial sums meet in the first CTA's shared memory (distributed shared memory), added in
+//             rank order, so the result does not depend on timing.
+//   epilogue  PLAIN   out[m, n] (bfloat16 or float)
+//             SWIGLU  W = [gate rows; up rows] ([2 I, K]); a CTA takes BN/2 gate rows and the same up rows
+//                     and writes silu(gate) * up (reference: src/layers/fused_ops.cu:142-144)
+//             QKV     BN = head_dim: a CTA owns one head of the packed q, k, v rows; per-head RMSNorm,
+//                     half-split rotary encoding, q to q_out, k and v into the paged cache (the work of
+//                     qkv_post.cu, with the same error flags).
+// Every wait on a barrier is bounded by the clock; a wait that runs out flags the engine's error word.
+#include <cooperative_groups.h>
+#include <cuda.h>
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+typedef __nv_bfloat16 bf16;
+
+constexpr int BK = 64;                 // k per stage: 128 bytes of a weight row
+constexpr int MMAX = 16;               // rows of x
+constexpr int WARPS = 4;
+constexpr int XS_BYTES = 64 * 1024;    // the rows of x' that a CTA multiplies with
+constexpr int W_RING_BYTES = 128 * 1024;
+
+enum : int { EPI_PLAIN_BF16 = 0, EPI_PLAIN_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+
+struct SkinnyParams {
+  // prologue
+  const bf16* x;            // [rows of x, K]
+  const int* x_rows;        // optional gather: row m of the product is x[x_rows[m]]
+  const bf16* residual;     // null: no norm prologue
+  bf16* residual_out;       // null: the sum is not stored
+  const void* norm_w;       // [K] bfloat16 or float
+  int norm_w_f32;
+  float eps;
+  // product
+  int M, N, K, ksplit;
+  // epilogue
+  int mode;
+  void* out;                // PLAIN: [M, N]; SWIGLU: [M, N / 2]; QKV: q_out [M, nh * d]
+  // QKV
+  int nh, nkv, rot_dim, max_pos, page_size;
+  long long cache_slots;
+  float qk_eps;
+  const void* q_w;          // [d] per-head norm weights (null: no norm), bfloat16 or float
+  const void* k_w;
+  int qk_w_f32;
+  const float* cos_table;   // [max_pos, rot_dim / 2] (null: no rotation)
+  const float* sin_table;
+  const int* positions;     // [M]
+  const int* slots;         // [M] (null: nothing is stored)
+  bf16* k_cache;            // [pages + 1, nkv, page_size, d]
+  bf16* v_cache;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t start = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_ns() - start > 1000000000ull) {
+      atomicOr(err, B200_ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float norm_weight(const void* w, int f32, int i) {
+  return f32 ? static_cast<const float*>(w)[i] : __bfloat162float(static_cast<const bf16*>(w)[i]);
+}
+
+// MT: 64-row units of the weight tile (BN = 64 MT rows; a warp owns 16 MT of them).
+template <int MT>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParams p) {
+  constexpr int BN = 64 * MT;
+  constexpr int STAGE_BYTES = BN * 128;
+  constexpr int STAGES = W_RING_BYTES / STAGE_BYTES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  bf16* xs = reinterpret_cast<bf16*>(ring + W_RING_BYTES);                     // [mpad][ldx]
+  float* red = reinterpret_cast<float*>(ring + W_RING_BYTES + XS_BYTES);       // [MMAX][BN + 1]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + MMAX * (BN + 1));
+  uint64_t* empty = full + STAGES;
+  float* row_scale = reinterpret_cast<float*>(empty + STAGES);                 // [MMAX]
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int tile = blockIdx.x / p.ksplit;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int M = p.M, K = p.K;
+  const int mpad = M <= 8 ? 8 : 16;
+  const int kblocks = (K + BK - 1) / BK;
+  const int kb_per = (kblocks + p.ksplit - 1) / p.ksplit;
+  const int kb_lo = min(kblocks, rank * kb_per), kb_hi = min(kblocks, kb_lo + kb_per);
+  const int nkb = kb_hi - kb_lo;
+  const int k_lo = kb_lo * BK, kc = nkb * BK;                                  // this CTA's columns, padded to 64
+  const int ldx = kc + 8;                                                      // padded row: conflict-free ldmatrix
+
+  if (threadIdx.x < STAGES) { mbar_init(full + threadIdx.x, 1); mbar_init(empty + threadIdx.x, WARPS); }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  __syncthreads();
+
+  // Weight rows of this tile: PLAIN / QKV: BN consecutive rows; SWIGLU: BN/2 gate rows, then the same up rows.
+  const int w_row0 = p.mode == EPI_SWIGLU ? tile * (BN / 2) : tile * BN;
+  const int up_row0 = p.N / 2 + tile * (BN / 2);
+  auto issue = [&](int j) {      // one thread: fetch k-block j of this CTA into its stage
+    const int s = j % STAGES;
+    unsigned char* dst = ring + s * STAGE_BYTES;
+    mbar_expect_tx(full + s, STAGE_BYTES);
+    if (p.mode == EPI_SWIGLU) {
+      tma_load_2d(dst, &wmap, (kb_lo + j) * BK, w_row0, full + s);
+      tma_load_2d(dst + STAGE_BYTES / 2, &wmap, (kb_lo + j) * BK, up_row0, full + s);
+    } else {
+      tma_load_2d(dst, &wmap, (kb_lo + j) * BK, w_row0, full + s);
+    }
+  };
+  // The weights do not depend on the prologue: start streaming them first.
+  if (threadIdx.x == 0)
+    for (int j = 0; j < STAGES - 1 && j < nkb; ++j) issue(j);
+
+  // ---- prologue: the rows of x' for columns [k_lo, k_lo + kc) as bfloat16 in shared memory
+  if (p.residual != nullptr) {
+    for (int m = warp; m < M; m += WARPS) {
+      const size_t src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K;
+      float ss = 0.0f;
+      for (int k = lane * 8; k < K; k += 32 * 8) {                             // K is a multiple of 8 (checked by the launcher)
+        float a[8], b[8];
+        Vec16<bf16>::load(p.x + src + k, a);
+        Vec16<bf16>::load(p.residual + src + k, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float s = a[i] + b[i]; ss += s * s; }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) row_scale[m] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+    }
+    __syncthreads();
+    const bool writer = blockIdx.x == 0 && p.residual_out != nullptr;
+    for (int m = warp; m < mpad; m += WARPS) {
+      const size_t src = m < M ? static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K : 0;
+      const float scale = m < M ? row_scale[m] : 0.0f;
+      // The writer CTA walks the whole row (it stores the new residual), the others only their columns.
+      const int k_begin = writer ? 0 : k_lo, k_end = writer ? max(K, k_lo + kc) : k_lo + kc;
+      for (int k = k_begin + lane * 8; k < k_end; k += 32 * 8) {
+        float a[8], b[8];
+        const bool live = m < M && k < K;
+        if (live) { Vec16<bf16>::load(p.x + src + k, a); Vec16<bf16>::load(p.residual + src + k, b); }
+        __align__(16) bf16 sum_rounded[8];
+        __align__(16) bf16 normed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float s = live ? a[i] + b[i] : 0.0f;
+          sum_rounded[i] = __float2bfloat16_rn(s);
+          normed[i] = __float2bfloat16_rn(live ? s * scale * norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f);
+        }
+        if (writer && live) *reinterpret_cast<uint4*>(p.residual_out + src + k) = *reinterpret_cast<uint4*>(sum_rounded);
+        if (k >= k_lo && k < k_lo + kc) *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(normed);
+      }
+    }
+  } else {
+    for (int m = warp; m < mpad; m += WARPS) {
+      const size_t src = m < M ? static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K : 0;
+      for (int k = k_lo + lane * 8; k < k_lo + kc; k += 32 * 8) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (m < M && k < K) v = *reinterpret_cast<const uint4*>(p.x + src + k);
+        *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = v;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- product: this warp's 16 MT weight rows against the rows of x'
+  float acc[MT][2][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int n = 0; n < 2; ++n) { acc[i][n][0] = acc[i][n][1] = acc[i][n][2] = acc[i][n][3] = 0.0f; }
+  const int mi = lane >> 3, r8 = lane & 7;
+  bool ok = true;
+  for (int it = 0; it < nkb; ++it) {
+    const int s = it % STAGES;
+    if (threadIdx.x == 0) {
+      const int j = it + STAGES - 1;
+      if (j < nkb) {
+        const int use = j / STAGES;
+        if (use > 0) ok = mbar_wait(empty + j % STAGES, (use - 1) & 1, p.err);
+        if (ok) issue(j);
+      }
+    }
+    if (!mbar_wait(full + s, (it / STAGES) & 1, p.err)) { ok = false; break; }
+    const unsigned char* wt = ring + s * STAGE_BYTES;
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
+      // B operand: x'[m][k], two 8-row groups (m 0..7, 8..15), k and k + 8
+      uint32_t b[4];
+      // (with 8 rows of x' only, the lanes of the second group point at the first: its result is not used)
+      ldmatrix_x4(b, xs + ((mpad > 8 ? (mi >> 1) * 8 : 0) + r8) * ldx + it * BK + ks * 16 + (mi & 1) * 8);
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        const int r = warp * (16 * MT) + i * 16 + (lane & 15);                 // weight row inside the tile
+        const int c = ks * 2 + (lane >> 4);                                    // 16-byte chunk of the 128-byte row
+        uint32_t a[4];
+        ldmatrix_x4(a, wt + r * 128 + ((c ^ (r & 7)) << 4));
+        mma_bf16(acc[i][0], a, b[0], b[1]);
+        if (mpad > 8) mma_bf16(acc[i][1], a, b[2], b[3]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + s);
+  }
+
+  // ---- the partial sums of the cluster meet in rank 0, added in rank order
+  const int g = lane >> 2, t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    const int n = warp * (16 * MT) + i * 16 + g;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int m = nt * 8 + t2;
+      if (m < mpad) {
+        red[m * (BN + 1) + n] = acc[i][nt][0];
+        red[(m + 1) * (BN + 1) + n] = acc[i][nt][1];
+        red[m * (BN + 1) + n + 8] = acc[i][nt][2];
+        red[(m + 1) * (BN + 1) + n + 8] = acc[i][nt][3];
+      }
+    }
+  }
+  cluster.sync();
+  if (rank == 0 && p.ksplit > 1) {
+    for (int i = threadIdx.x; i < mpad * BN; i += blockDim.x) {
+      const int m = i / BN, n = i - m * BN;
+      float sum = red[m * (BN + 1) + n];
+      for (int r = 1; r < p.ksplit; ++r) sum += cluster.map_shared_rank(red, r)[m * (BN + 1) + n];
+      red[m * (BN + 1) + n] = sum;
+    }
+  }
+  cluster.sync();                    // the others' shared memory has been read: they may leave
+  if (rank != 0 || !ok) return;
+
+  // ---- epilogue on red[m][n] (float)
+  if (p.mode == EPI_PLAIN_BF16 || p.mode == EPI_PLAIN_F32) {
+    for (int i = threadIdx.x; i < M * BN; i += blockDim.x) {
+      const int m = i / BN, n = i - m * BN, col = tile * BN + n;
+      if (col >= p.N) continue;
+      const float v = red[m * (BN + 1) + n];
+      if (p.mode == EPI_PLAIN_F32) static_cast<float*>(p.out)[static_cast<size_t>(m) * p.N + col] = v;
+      else static_cast<bf16*>(p.out)[static_cast<size_t>(m) * p.N + col] = __float2bfloat16_rn(v);
+    }
+  } else if (p.mode == EPI_SWIGLU) {
+    const int inter = p.N / 2;
+    for (int i = threadIdx.x; i < M * (BN / 2); i += blockDim.x) {
+      const int m = i / (BN / 2), n = i - m * (BN / 2), col = tile * (BN / 2) + n;
+      if (col >= inter) continue;
+      // gate and up leave the product as bfloat16 values in the unfused path; the same rounding here
+      const float gate = __bfloat162float(__float2bfloat16_rn(red[m * (BN + 1) + n]));
+      const float up = __bfloat162float(__float2bfloat16_rn(red[m * (BN + 1) + BN / 2 + n]));
+      static_cast<bf16*>(p.out)[static_cast<size_t>(m) * inter + col] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+    }
+  } else {                                                                   // EPI_QKV: tile = one head, BN = head_dim
+    constexpr int d = BN;
+    const int head = tile;
+    const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+    for (int m = warp; m < M; m += WARPS) {
+      float* row = red + m * (BN + 1);
+      // the projection's output is a bfloat16 tensor in the unfused path; the same rounding here
+      for (int i = lane; i < d; i += 32) row[i] = __bfloat162float(__float2bfloat16_rn(row[i]));
+      __syncwarp();
+      bf16* dst;
+      if (is_q) {
+        dst = static_cast<bf16*>(p.out) + (static_cast<size_t>(m) * p.nh + head) * d;
+      } else {
+        if (p.slots == nullptr) continue;
+        const int slot = p.slots[m];
+        if (slot == 0) continue;
+        if (slot < 0 || slot >= p.cache_slots) { if (lane == 0) atomicOr(p.err, B200_ERR_SLOT_RANGE); continue; }
+        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+        const int page = slot / p.page_size, offset = slot - page * p.page_size;
+        dst = (is_k ? p.k_cache : p.v_cache) + ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + offset) * d;
+      }
+      if (!is_q && !is_k) {
+        for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
+        continue;
+      }
+      const void* w = is_q ? p.q_w : p.k_w;
+      if (w != nullptr) {
+        float ss = 0.0f;
+        for (int i = lane; i < d; i += 32) ss += row[i] * row[i];
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / static_cast<float>(d) + p.qk_eps);
+        for (int i = lane; i < d; i += 32) row[i] = row[i] * scale * norm_weight(w, p.qk_w_f32, i);
+        __syncwarp();
+      }
+      const int half = p.rot_dim / 2;
+      bool rotate = p.cos_table != nullptr && half > 0;
+      int pos = 0;
+      if (rotate) {
+        pos = p.positions[m];
+        if (pos < 0 || pos >= p.max_pos) { if (lane == 0) atomicOr(p.err, B200_ERR_POSITION_RANGE); rotate = false; }
+      }
+      if (rotate) {
+        const float* c = p.cos_table + static_cast<size_t>(pos) * half;
+        const float* s = p.sin_table + static_cast<size_t>(pos) * half;
+        for (int i = lane; i < half; i += 32) {
+          const float a = row[i], b = row[i + half];
+          dst[i] = __float2bfloat16_rn(a * c[i] - b * s[i]);
+          dst[i + half] = __float2bfloat16_rn(b * c[i] + a * s[i]);
+        }
+        for (int i = p.rot_dim + lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
+      } else {
+        for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Writes into `out_map` (128 bytes) the TMA descriptor of a bfloat16 weight matrix [n, k], fetched in boxes of
+// `box_rows` rows x 64 columns with the 128-byte swizzle.  Rows beyond n and columns beyond k read as zeros.
+B200_EXPORT int b200_weight_tensor_map(void* out_map, const void* weight, long long n, long long k, int box_rows) {
+  if (n <= 0 || k <= 0 || box_rows <= 0 || box_rows > 256 || k % 8 != 0) return B200_BAD_SIZE;
+  if (reinterpret_cast<uintptr_t>(weight) % 16 != 0) return B200_BAD_ALIGN;
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (fn == nullptr || found != cudaDriverEntryPointSuccess) return static_cast<int>(cudaErrorNotSupported);
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(n)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * sizeof(bf16)};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(weight), dims, strides, box, elem_strides,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 1000 + static_cast<int>(r);
+  memcpy(out_map, &map, sizeof(map));
+  return 0;
+}
+
+// Rows of the weight tile that a CTA owns in `mode` for head size `head_dim` (QKV only): 64, 128 or 256; 0: refused.
+B200_EXPORT int b200_skinny_tile_rows(int mode, int head_dim) {
+  if (mode != EPI_QKV) return 128;
+  return (head_dim == 64 || head_dim == 128 || head_dim == 256) ? head_dim : 0;
+}
+
+// Rows of a weight box that b200_weight_tensor_map must be given for `mode`.
+B200_EXPORT int b200_skinny_box_rows(int mode, int head_dim) {
+  const int bn = b200_skinny_tile_rows(mode, head_dim);
+  return mode == EPI_SWIGLU ? bn / 2 : bn;
+}
+
+// Largest K range of one CTA for `m` rows, and from it the smallest cluster; 0: the product is refused.
+static int choose_ksplit(int m, int n_tiles, int k, int sm_count) {
+  const int mpad = m <= 8 ? 8 : 16;
+  const int kc_max = ((XS_BYTES / (mpad * 2)) - 8) / BK * BK;
+  const int kblocks = (k + BK - 1) / BK;
+  int need = (k + kc_max - 1) / kc_max;
+  if (need > 8) return 0;
+  // More CTAs while SMs are idle, as long as every CTA keeps at least four k-blocks.
+  int split = need;
+  while (split < 8 && n_tiles * split < sm_count && kblocks / (split * 2) >= 4) split *= 2;
+  if (split > 8) split = 8;
+  return split < 1 ? 1 : split;
+}
+
+template <int MT>
+static int launch(const CUtensorMap& map, const SkinnyParams& p, int n_tiles, cudaStream_t stream) {
+  constexpr int BN = 64 * MT;
+  constexpr int STAGES = W_RING_BYTES / (BN * 128);
+  const size_t smem = 1024 + W_RING_BYTES + XS_BYTES + MMAX * (BN + 1) * sizeof(float) + 2 * STAGES * sizeof(uint64_t) +
+                      MMAX * sizeof(float) + 64;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_linear_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(n_tiles * p.ksplit);
+  config.blockDim = dim3(WARPS * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.ksplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, skinny_linear_kernel<MT>, map, p);
+  return e == cudaSuccess ? b200_check_launch() : static_cast<int>(e);
+}
+
+// `params`: a SkinnyParams filled by the caller (ksplit is chosen here); `w_map`: the descriptor of the weight.
+// Refuses (B200_BAD_SIZE) more than 16 rows, a K that is no multiple of 8 or too long for a cluster of 8, and
+// head sizes other than 64 / 128 / 256 in QKV mode.
+B200_EXPORT int b200_skinny_linear(const void* w_map, const void* params, int head_dim, int sm_count, cudaStream_t stream) {
+  SkinnyParams p;
+  memcpy(&p, params, sizeof(p));
+  if (p.M <= 0) return 0;
+  if (p.M > MMAX || p.N <= 0 || p.K <= 0 || p.K % 8 != 0) return B200_BAD_SIZE;
+  if (p.mode < EPI_PLAIN_BF16 || p.mode > EPI_QKV) return B200_BAD_SIZE;
+  if (p.mode == EPI_SWIGLU && p.N % 2 != 0) return B200_BAD_SIZE;
+  const int bn = b200_skinny_tile_rows(p.mode, head_dim);
+  if (bn == 0) return B200_BAD_SIZE;
+  if (p.mode == EPI_QKV && (p.N != (p.nh + 2 * p.nkv) * head_dim || p.rot_dim < 0 || p.rot_dim > head_dim || (p.rot_dim & 1)))
+    return B200_BAD_SIZE;
+  const int cols = p.mode == EPI_SWIGLU ? p.N / 2 : p.N;
+  const int tile_cols = p.mode == EPI_SWIGLU ? bn / 2 : bn;
+  const int n_tiles = (cols + tile_cols - 1) / tile_cols;
+  p.ksplit = choose_ksplit(p.M, n_tiles, p.K, sm_count > 0 ? sm_count : 148);
+  if (p.ksplit == 0) return B200_BAD_SIZE;
+  CUtensorMap map;
+  memcpy(&map, w_map, sizeof(map));
+  if (bn == 64) return launch<1>(map, p, n_tiles, stream);
+  if (bn == 128) return launch<2>(map, p, n_tiles, stream);
+  return launch<4>(map, p, n_tiles, stream);
+}
+
+B200_EXPORT int b200_skinny_params_size() { return static_cast<int>(sizeof(SkinnyParams)); }

@@ -325,6 +325,167 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     _ok(rc, "decode_attention", 2 if splits > 1 else 1)
 
 
+# --------------------------------------------------------------------------- few-row products with fused ends
+SKINNY_MAX_ROWS = 16
+EPI_PLAIN_BF16, EPI_PLAIN_F32, EPI_SWIGLU, EPI_QKV = 0, 1, 2, 3
+
+
+class _SkinnyParams(ctypes.Structure):
+    """Mirror of ``SkinnyParams`` in csrc/skinny_linear.cu (same order, native alignment)."""
+    _fields_ = [("x", ctypes.c_void_p), ("x_rows", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+                ("residual_out", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("norm_w_f32", ctypes.c_int),
+                ("eps", ctypes.c_float), ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("ksplit", ctypes.c_int), ("mode", ctypes.c_int), ("out", ctypes.c_void_p),
+                ("nh", ctypes.c_int), ("nkv", ctypes.c_int), ("rot_dim", ctypes.c_int), ("max_pos", ctypes.c_int),
+                ("page_size", ctypes.c_int), ("cache_slots", ctypes.c_longlong), ("qk_eps", ctypes.c_float),
+                ("q_w", ctypes.c_void_p), ("k_w", ctypes.c_void_p), ("qk_w_f32", ctypes.c_int),
+                ("cos_table", ctypes.c_void_p), ("sin_table", ctypes.c_void_p), ("positions", ctypes.c_void_p),
+                ("slots", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("err", ctypes.c_void_p)]
+
+
+class PendingNorm:
+    """A residual add + RMSNorm that has not run: the product that consumes it runs it as its prologue.
+
+    ``residual_out`` is the tensor that will hold the rounded sum (None: the sum is not kept).
+    ``materialize()`` runs the norm as a kernel of its own, for a consumer that cannot fuse it.
+    """
+
+    def __init__(self, x, residual, weight, eps, rows=None, write_residual=True):
+        self.x, self.residual, self.weight, self.eps, self.rows = x, residual, weight, float(eps), rows
+        self.residual_out = torch.empty_like(residual) if write_residual else None
+        self.dtype, self.device = x.dtype, x.device
+        n = x.shape[0] if rows is None else rows.numel()
+        self.shape = (n, x.shape[-1])
+
+    def materialize(self) -> torch.Tensor:
+        if self.residual_out is not None:
+            self.residual_out.copy_(self.residual)
+            return add_rms_norm(self.x, self.residual_out, self.weight, self.eps, rows=self.rows)
+        return add_rms_norm(self.x, self.residual, self.weight, self.eps, rows=self.rows, write_residual=False)
+
+
+_weight_maps = {}
+_sm_counts = {}
+
+
+def _skinny():
+    lib = load_cuda_library("skinny_linear.cu")
+    if not getattr(lib, "_checked", False):
+        if lib.b200_skinny_params_size() != ctypes.sizeof(_SkinnyParams):
+            raise KernelError("the parameter block of skinny_linear.cu and its Python mirror differ")
+        lib._checked = True
+    return lib
+
+
+def _weight_map(weight: torch.Tensor, box_rows: int):
+    key = (weight.data_ptr(), tuple(weight.shape), box_rows)
+    buf = _weight_maps.get(key)
+    if buf is None:
+        buf = ctypes.create_string_buffer(128)
+        rc = _skinny().b200_weight_tensor_map(buf, _p(weight), ctypes.c_longlong(weight.shape[0]),
+                                              ctypes.c_longlong(weight.shape[1]), box_rows)
+        if rc != 0:
+            raise KernelError(f"the TMA descriptor of a weight matrix could not be made (code {rc})")
+        if len(_weight_maps) > 8192:
+            _weight_maps.clear()
+        _weight_maps[key] = buf
+    return buf
+
+
+def skinny_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
+              head_dim: int = 0) -> bool:
+    """Whether the few-row kernel takes this product: bfloat16 activations and weight, at most 16 rows,
+    K a multiple of 8 and at most 8 x 4032 (8 rows) or 8 x 1984 (16 rows); QKV: head size 64, 128 or 256."""
+    if act_dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.dim() != 2:
+        return False
+    k = weight.shape[1]
+    if not 0 < rows <= SKINNY_MAX_ROWS or k % 8 or not weight.is_contiguous() or weight.data_ptr() % 16:
+        return False
+    if k > 8 * (4032 if rows <= 8 else 1984):
+        return False
+    if mode == EPI_QKV and head_dim not in (64, 128, 256):
+        return False
+    if mode == EPI_SWIGLU and weight.shape[0] % 2:
+        return False
+    return True
+
+
+def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
+                  qkv: Optional[dict] = None) -> torch.Tensor:
+    """epilogue(prologue(x) . weight^T) for at most 16 rows, in one kernel.
+
+    ``x``: a bfloat16 tensor [rows, K], or a ``PendingNorm`` (then the residual add and the norm run as the
+    prologue and ``x.residual_out`` is filled).  ``mode``: EPI_PLAIN_BF16 / EPI_PLAIN_F32: the product;
+    EPI_SWIGLU: silu(gate) * up for a weight of gate rows then up rows; EPI_QKV: per-head norm, rotary
+    encoding and the cache store, with ``qkv`` = the keyword arguments of ``qkv_post`` (without ``qkv``);
+    the result is then ``q_out``.
+    """
+    pending = x if isinstance(x, PendingNorm) else None
+    src = pending.x if pending is not None else x
+    rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
+    _cuda(src, weight, rows_t)
+    _contig(src, weight, rows_t)
+    m = src.shape[0] if rows_t is None else rows_t.numel()
+    n, k = weight.shape
+    if src.shape[-1] != k:
+        raise KernelError(f"the rows have {src.shape[-1]} columns, the weight has {k}")
+    head_dim = qkv["head_dim"] if qkv else 0
+    if not skinny_ok(m, weight, src.dtype, mode, head_dim):
+        raise KernelError("the few-row product refuses this size or dtype")
+    lib = _skinny()
+    P = _SkinnyParams()
+    P.x, P.x_rows = src.data_ptr(), (0 if rows_t is None else rows_t.data_ptr())
+    if pending is not None:
+        if pending.residual.dtype != torch.bfloat16 or pending.residual.shape != src.shape:
+            raise KernelError("the residual must be bfloat16 and have the shape of x")
+        P.residual = pending.residual.data_ptr()
+        P.residual_out = 0 if pending.residual_out is None else pending.residual_out.data_ptr()
+        P.norm_w, P.norm_w_f32, P.eps = pending.weight.data_ptr(), int(pending.weight.dtype == torch.float32), pending.eps
+        if pending.weight.numel() != k or pending.weight.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("the norm weight must have K elements, bfloat16 or float32")
+    P.M, P.N, P.K, P.mode = m, n, k, mode
+    dev = src.device
+    P.err = error_word(dev).data_ptr()
+    if mode == EPI_QKV:
+        nh, nkv = qkv["num_heads"], qkv["num_kv_heads"]
+        out = qkv["q_out"]
+        kc, vc = qkv.get("k_cache"), qkv.get("v_cache")
+        qw, kw = qkv.get("q_weight"), qkv.get("k_weight")
+        cos, sin = qkv.get("cos"), qkv.get("sin")
+        slots = qkv.get("slots")
+        _cuda(out, kc, vc, qw, kw, cos, sin, qkv["positions"], slots)
+        if n != (nh + 2 * nkv) * head_dim or out.shape != (m, nh * head_dim) or out.dtype != torch.bfloat16:
+            raise KernelError("qkv sizes do not fit the weight")
+        if slots is not None and (kc is None or kc.dtype != torch.bfloat16 or kc.shape[1] != nkv or kc.shape[3] != head_dim):
+            raise KernelError("the cache must be bfloat16 [pages + 1, kv_heads, page_size, head_dim]")
+        if (qw is None) != (kw is None) or (qw is not None and qw.dtype != kw.dtype):
+            raise KernelError("q and k norm weights come together and share a dtype")
+        P.nh, P.nkv, P.rot_dim = nh, nkv, int(qkv.get("rot_dim", 0))
+        P.max_pos = 0 if cos is None else cos.shape[0]
+        P.page_size = 1 if kc is None else kc.shape[2]
+        P.cache_slots = 0 if kc is None else kc.shape[0] * kc.shape[2]
+        P.qk_eps = float(qkv.get("eps", 0.0))
+        P.q_w, P.k_w = (0 if qw is None else qw.data_ptr()), (0 if kw is None else kw.data_ptr())
+        P.qk_w_f32 = int(qw is not None and qw.dtype == torch.float32)
+        P.cos_table, P.sin_table = (0 if cos is None else cos.data_ptr()), (0 if sin is None else sin.data_ptr())
+        P.positions = qkv["positions"].data_ptr()
+        P.slots = 0 if slots is None else slots.data_ptr()
+        P.k_cache, P.v_cache = (0 if kc is None else kc.data_ptr()), (0 if vc is None else vc.data_ptr())
+    elif mode == EPI_SWIGLU:
+        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=dev)
+    else:
+        out = torch.empty((m, n), dtype=torch.float32 if mode == EPI_PLAIN_F32 else torch.bfloat16, device=dev)
+    P.out = out.data_ptr()
+    box = lib.b200_skinny_box_rows(mode, head_dim)
+    key = dev.index or 0
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(dev).multi_processor_count
+    rc = lib.b200_skinny_linear(_weight_map(weight, box), ctypes.byref(P), head_dim, _sm_counts[key], _stream())
+    _ok(rc, "skinny_linear")
+    return out
+
+
 # --------------------------------------------------------------------------- matrix products
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a[M, K] . w[N, K]^T in true 32-bit on CUDA cores."""
@@ -353,6 +514,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return cast(gemm_f32(x, weight), out_dtype)
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         _cuda(x, weight)
+        if out_dtype in (torch.bfloat16, torch.float32) and x.dim() == 2 and x.is_contiguous() \
+                and skinny_ok(x.shape[0], weight, x.dtype):
+            return skinny_linear(x, weight, EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16)
         if out_dtype == torch.bfloat16:
             return torch.mm(x, weight.t())
         return torch.mm(x, weight.t(), out_dtype=out_dtype)

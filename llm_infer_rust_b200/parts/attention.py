@@ -75,16 +75,30 @@ class GQAttention(Part):
     def state_spec(self):
         return None
 
+    def takes_pending(self, tokens: int) -> bool:
+        """Whether a step of ``tokens`` tokens runs the input norm as the prologue of the QKV product."""
+        return ops.skinny_ok(tokens, self.params["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d)
+
     def forward(self, x, ctx, cache):
         p = self.params
         tokens = x.shape[0]
-        qkv = ops.linear(x, p["qkv_proj"])
-        q = torch.empty((tokens, self.nh * self.d), dtype=x.dtype, device=x.device)
         rope = self.rope
-        ops.qkv_post(qkv, q, cache.k, cache.v, p.get("q_norm"), p.get("k_norm"),
-                     float(self.qk_eps or 0.0), rope.cos if rope else None, rope.sin if rope else None,
-                     rope.rot_dim if rope else 0, ctx.positions,
-                     ctx.slots[cache.group] if cache.writes else None, self.nh, self.nkv, self.d)
+        q = torch.empty((tokens, self.nh * self.d), dtype=x.dtype, device=x.device)
+        slots = ctx.slots[cache.group] if cache.writes else None
+        if self.takes_pending(tokens):
+            # few tokens: norm (if pending), projection, per-head norm, rotation and cache store in one kernel
+            ops.skinny_linear(x, p["qkv_proj"], ops.EPI_QKV, qkv=dict(
+                head_dim=self.d, num_heads=self.nh, num_kv_heads=self.nkv, q_out=q, k_cache=cache.k, v_cache=cache.v,
+                q_weight=p.get("q_norm"), k_weight=p.get("k_norm"), eps=float(self.qk_eps or 0.0),
+                cos=rope.cos if rope else None, sin=rope.sin if rope else None,
+                rot_dim=rope.rot_dim if rope else 0, positions=ctx.positions, slots=slots))
+        else:
+            if isinstance(x, ops.PendingNorm):
+                x = x.materialize()
+            qkv = ops.linear(x, p["qkv_proj"])
+            ops.qkv_post(qkv, q, cache.k, cache.v, p.get("q_norm"), p.get("k_norm"),
+                         float(self.qk_eps or 0.0), rope.cos if rope else None, rope.sin if rope else None,
+                         rope.rot_dim if rope else 0, ctx.positions, slots, self.nh, self.nkv, self.d)
         out = torch.empty_like(q)
         g = cache.group
         page = ctx.page_sizes[g]

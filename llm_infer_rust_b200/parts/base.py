@@ -15,6 +15,11 @@ Categories and the interface each must have:
                       values it needs, or None); ``state_spec()`` (fixed-size
                       per-request state it needs, or None)
 ``feed_forward``      ``forward(x) -> y``
+
+Optional, for fusion across parts: a norm may offer ``pending_add(x, residual, ...)``, which
+returns the add + norm unrun (``ops.PendingNorm``); a mixer, feed-forward or head that offers
+``takes_pending(tokens) -> bool`` and answers True is then given that object as ``x`` and runs it
+as the prologue of its first product.  Parts without these methods get plain tensors.
 ``block``             built from a ``LayerSpec``; ``forward(h, residual, ctx, cache) -> (h, residual)``
 ``embedding``         ``forward(token_ids) -> h``
 ``head``              ``forward(x) -> float32 logits``

@@ -27,14 +27,28 @@ class PreNormDeferredAdd:
         return {"input_norm": self.input_norm, "mixer": self.mixer,
                 "post_mixer_norm": self.post_mixer_norm, "feed_forward": self.feed_forward}
 
+    @staticmethod
+    def _fuses(norm, consumer, tokens):
+        """A norm is handed on unrun when it can be (``pending_add``) and its consumer ``takes_pending``."""
+        takes = getattr(consumer, "takes_pending", None)
+        return hasattr(norm, "pending_add") and takes is not None and takes(tokens)
+
     def forward(self, h, residual, ctx, cache):
+        tokens = h.shape[0]
         if residual is None:
             residual = h
             x = self.input_norm.forward(h)
+        elif self._fuses(self.input_norm, self.mixer, tokens):
+            x = self.input_norm.pending_add(h, residual)
+            residual = x.residual_out
         else:
             x = self.input_norm.forward_add(h, residual, out=h)
         a = self.mixer.forward(x, ctx, cache)
-        x = self.post_mixer_norm.forward_add(a, residual, out=a)
+        if self._fuses(self.post_mixer_norm, self.feed_forward, tokens):
+            x = self.post_mixer_norm.pending_add(a, residual)
+            residual = x.residual_out
+        else:
+            x = self.post_mixer_norm.forward_add(a, residual, out=a)
         return self.feed_forward.forward(x), residual
 
 

@@ -40,7 +40,14 @@ class LinearHead(Part):
     def param_decls(self):
         return {"weight": ParamDecl((self.vocab, self.hidden))}
 
+    def takes_pending(self, rows: int) -> bool:
+        return ops.skinny_ok(rows, self.params["weight"], self.env.dtype, ops.EPI_PLAIN_F32)
+
     def forward(self, x):
+        if isinstance(x, ops.PendingNorm):
+            if self.takes_pending(x.shape[0]):
+                return ops.skinny_linear(x, self.params["weight"], ops.EPI_PLAIN_F32)
+            x = x.materialize()
         return ops.linear(x, self.params["weight"], out_dtype=torch.float32)
 
 

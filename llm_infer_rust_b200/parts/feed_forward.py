@@ -23,7 +23,16 @@ class SwiGLU(Part):
         return {"gate_up_proj": ParamDecl((2 * self.inter, self.hidden)),
                 "down_proj": ParamDecl((self.hidden, self.inter))}
 
+    def takes_pending(self, tokens: int) -> bool:
+        """Whether a step of ``tokens`` tokens runs the norm before it as the prologue of the gate/up product."""
+        return ops.skinny_ok(tokens, self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU)
+
     def forward(self, x):
+        if self.takes_pending(x.shape[0]):
+            # few tokens: norm (if pending), gate and up projections and silu(gate) * up in one kernel
+            return ops.linear(ops.skinny_linear(x, self.params["gate_up_proj"], ops.EPI_SWIGLU), self.params["down_proj"])
+        if isinstance(x, ops.PendingNorm):
+            x = x.materialize()
         gate_up = ops.linear(x, self.params["gate_up_proj"])
         return ops.linear(ops.silu_mul(gate_up), self.params["down_proj"])
 

@@ -82,8 +82,11 @@ class DecoderModel:
         residual = None
         for e, entry in enumerate(self.run_list):
             h, residual = self.blocks[entry.layer].forward(h, residual, ctx, caches[e])
+        takes = getattr(self.lm_head, "takes_pending", None)
         if residual is None:
             x = self.final_norm.forward(h, rows=ctx.logit_rows)
+        elif hasattr(self.final_norm, "pending_add") and takes is not None and takes(ctx.num_logits):
+            x = self.final_norm.pending_add(h, residual, rows=ctx.logit_rows, write_residual=False)
         else:
             x = self.final_norm.forward_add(h, residual, rows=ctx.logit_rows, write_residual=False)
         return self.lm_head.forward(x)

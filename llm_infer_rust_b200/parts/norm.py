@@ -30,5 +30,11 @@ class RMSNorm(Part):
         return ops.add_rms_norm(x, residual, self.params["weight"], self.eps, out=out, rows=rows,
                                 write_residual=write_residual)
 
+    def pending_add(self, x, residual, rows=None, write_residual=True):
+        """The same add + norm, not run yet: a consumer that ``takes_pending`` fuses it into its product.
+        The new residual will be in ``.residual_out`` of the result (``residual`` itself is left alone)."""
+        return ops.PendingNorm(x, residual, self.params["weight"], self.eps, rows=rows,
+                               write_residual=write_residual)
+
 
 register_part("norm", "rms_norm", RMSNorm)

@@ -60,6 +60,12 @@ TINY = {
                         layer_types=["sliding_attention", "full_attention", "sliding_attention",
                                      "full_attention"]),
               seed=2, norm_std=0.05, page_size=8),
+    # D has a head size (64) for which the bfloat16 engine fuses norm, QKV product, per-head norm, rotation
+    # and cache store into one kernel when a step brings few tokens.
+    "D": dict(raw=_base(num_hidden_layers=2, hidden_size=136, num_attention_heads=4, num_key_value_heads=2,
+                        head_dim=64, intermediate_size=200, vocab_size=333, rope_theta=1e5,
+                        rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=256),
+              seed=3, norm_std=0.1, page_size=16),
 }
 
 

@@ -129,6 +129,111 @@ def test_linear_bf16_and_mixed(m, n, k):
     close(o.linear(x, w.float()), R.ref_linear(x, w), torch.bfloat16)
 
 
+def _bf(t):
+    return t.to(torch.bfloat16).float()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (5, 509, 96), (8, 1000, 1024), (13, 130, 3000), (16, 256, 2048),
+                                   (3, 96, 12288), (16, 64, 12288), (2, 4000, 40)])
+@pytest.mark.parametrize("with_norm", [False, True])
+def test_few_row_product_plain(m, n, k, with_norm):
+    """x . W^T for at most 16 rows, alone and with the residual add + norm as its prologue, in both output dtypes,
+    with a gather of the rows; K long enough for a cluster to split it, N and K off every tile size."""
+    o = ops()
+    x, w = rnd(m + 3, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1, scale=0.05)
+    rows = torch.tensor([(3 * i + 1) % (m + 3) for i in range(m)], dtype=torch.int32, device=DEV)
+    res = rnd(m + 3, k, dtype=torch.bfloat16, seed=2)
+    nw = (1 + 0.1 * rnd(k, seed=3)).to(torch.bfloat16)
+    for gather in (False, True):
+        sel = rows.long() if gather else torch.arange(m, device=DEV)
+        if with_norm:
+            src = o.PendingNorm(x if gather else x[:m].contiguous(), res if gather else res[:m].contiguous(), nw, 1e-5,
+                                rows=rows if gather else None, write_residual=not gather)
+            s_sum = x[sel].float() + res[sel].float()
+            xin = _bf(s_sum * torch.rsqrt((s_sum * s_sum).mean(-1, keepdim=True) + 1e-5) * nw.float())
+        else:
+            src = x if gather else x[:m].contiguous()
+            xin = x[sel].float()
+        want = xin @ w.float().t()
+        for mode, dtype in ((o.EPI_PLAIN_F32, torch.float32), (o.EPI_PLAIN_BF16, torch.bfloat16)):
+            got = o.skinny_linear(src, w, mode, x_rows=rows if (gather and not with_norm) else None)
+            assert got.dtype == dtype and tuple(got.shape) == (m, n)
+            scale = max(1.0, float(want.abs().max()))
+            tol = 2e-3 * scale if dtype == torch.float32 else 2.0 ** -7 * scale
+            assert (got.float() - want).abs().max() <= tol, (mode, gather)
+        if with_norm and not gather:
+            assert torch.equal(src.residual_out, s_sum.to(torch.bfloat16))         # the rounded sum is the new residual
+            assert torch.equal(src.residual, res[:m])                              # the old one is left alone
+    o.check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 224, 96), (16, 3072, 1024), (4, 100, 4096)])
+def test_few_row_product_swiglu(m, inter, k):
+    o = ops()
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.1)
+    got = o.skinny_linear(x, w, o.EPI_SWIGLU)
+    gu = _bf(x.float() @ w.float().t())
+    want = R.ref_silu_mul(gu.to(torch.bfloat16))
+    assert tuple(got.shape) == (m, inter)
+    assert (got.float() - want.float()).abs().max() <= 2.0 ** -6 * max(1.0, float(want.float().abs().max()))
+
+
+@pytest.mark.parametrize("m,nh,nkv,d,k,with_norm", [(1, 4, 2, 64, 128, True), (9, 16, 8, 128, 1024, True),
+                                                    (16, 3, 1, 64, 200, False), (5, 2, 2, 256, 512, True)])
+def test_few_row_product_qkv(m, nh, nkv, d, k, with_norm):
+    """The fused QKV step against the separate kernels' references: projection, per-head norm, rotation, store."""
+    o = ops()
+    page, pages, max_pos, eps = 8, 6, 64, 1e-6
+    n = (nh + 2 * nkv) * d
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1, scale=0.1)
+    res = rnd(m, k, dtype=torch.bfloat16, seed=2)
+    nw = (1 + 0.1 * rnd(k, seed=3)).to(torch.bfloat16)
+    qw, kw = (1 + 0.2 * rnd(d, seed=4)).to(torch.bfloat16), (1 + 0.2 * rnd(d, seed=5)).float()
+    kw = kw.to(torch.bfloat16)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * \
+        torch.exp(torch.arange(0, d, 2, dtype=torch.float64) * (-math.log(1e4) / d))[None]
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    g = torch.Generator().manual_seed(6)
+    positions = torch.randint(0, max_pos, (m,), generator=g).to(torch.int32).to(DEV)
+    slots = (torch.randperm(page * pages, generator=g)[:m] + page).to(torch.int32)
+    if m > 2:
+        slots[2] = 0
+    slots = slots.to(DEV)
+    kc = torch.full((pages + 1, nkv, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    vc = torch.full_like(kc, 7.0)
+    q = torch.empty(m, nh * d, dtype=torch.bfloat16, device=DEV)
+    if with_norm:
+        src = o.PendingNorm(x, res, nw, 1e-5)
+        s_sum = x.float() + res.float()
+        xin = _bf(s_sum * torch.rsqrt((s_sum * s_sum).mean(-1, keepdim=True) + 1e-5) * nw.float())
+    else:
+        src, xin = x, x.float()
+    out = o.skinny_linear(src, w, o.EPI_QKV, qkv=dict(head_dim=d, num_heads=nh, num_kv_heads=nkv, q_out=q, k_cache=kc,
+                                                      v_cache=vc, q_weight=qw, k_weight=kw, eps=eps, cos=cos, sin=sin,
+                                                      rot_dim=d, positions=positions, slots=slots))
+    assert out is q
+    qkv = (xin @ w.float().t()).to(torch.bfloat16)
+    rq, rk, rv = R.ref_qkv_post(qkv, qw, kw, eps, cos, sin, d, positions, nh, nkv, d)
+    want_k, want_v = torch.full_like(kc, 7.0), torch.full_like(vc, 7.0)
+    R.ref_store_kv(want_k, want_v, rk, rv, slots)
+    # the projection is rounded to bfloat16 on both sides, but from sums in another order: one more ulp
+    for got, want in ((q.view(m, nh, d), rq), (kc, want_k), (vc, want_v)):
+        torch.testing.assert_close(got.float(), want.float(), atol=2.0 ** -6 * max(1.0, float(want.float().abs().max())), rtol=2.0 ** -6)
+    assert (kc[0] == 7.0).all() and (vc[0] == 7.0).all()
+    o.check_errors(torch.device(DEV))
+
+
+def test_few_row_product_refusals():
+    o = ops()
+    w = rnd(64, 64, dtype=torch.bfloat16)
+    assert not o.skinny_ok(17, w, torch.bfloat16) and not o.skinny_ok(4, w.float(), torch.bfloat16)
+    assert not o.skinny_ok(4, rnd(64, 60, dtype=torch.bfloat16), torch.bfloat16)          # K no multiple of 8
+    assert not o.skinny_ok(4, w, torch.bfloat16, o.EPI_QKV, 48) and o.skinny_ok(4, w, torch.bfloat16, o.EPI_QKV, 64)
+    assert not o.skinny_ok(16, rnd(8, 16384, dtype=torch.bfloat16), torch.bfloat16)       # too long for a cluster of 8
+    with pytest.raises(o.KernelError, match="refuses"):
+        o.skinny_linear(rnd(17, 64, dtype=torch.bfloat16), w)
+
+
 QKV_CASES = [  # nh, nkv, d, rot, eps, with_norm
     (4, 2, 16, 16, 1e-6, True), (6, 2, 32, 32, 1e-5, True), (5, 5, 48, 48, 3e-6, True),
     (8, 1, 128, 128, 1e-6, True), (3, 3, 80, 32, 1e-6, True), (2, 1, 64, 64, 1e-6, False),
