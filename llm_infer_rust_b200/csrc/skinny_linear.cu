@@ -9,6 +9,8 @@
 //             brings boxes of BN rows x 64 columns (128-byte swizzle) into a ring of stages, the rows of
 //             x' (at most 16) wait in shared memory, and mma.sync m16n8k16 multiplies with the WEIGHT rows
 //             on the 16-row side of the instruction, so no tensor work is wasted on padding the rows.
+//             A CTA has four groups of four warps (group g multiplies the k-blocks g, g + 4, ...; the groups'
+//             sums are added at the end) and one more warp that only feeds the ring.
 //             Where N / BN alone would leave SMs idle, a thread-block cluster of up to 8 CTAs splits K; the
 //             partial sums meet in the first CTA's shared memory (distributed shared memory), added in
 //             rank order, so the result does not depend on timing.
@@ -31,7 +33,10 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int BK = 64;                 // k per stage: 128 bytes of a weight row
 constexpr int MMAX = 16;               // rows of x
-constexpr int WARPS = 4;
+constexpr int ROW_WARPS = 4;           // warps that share the weight rows of a tile
+constexpr int GROUPS = 4;              // groups of ROW_WARPS warps; group g multiplies the k-blocks g, g + 4, ...
+constexpr int WARPS = ROW_WARPS * GROUPS;          // consumer warps; one more warp feeds the ring
+constexpr int THREADS = (WARPS + 1) * 32;
 constexpr int XS_BYTES = 64 * 1024;    // the rows of x' that a CTA multiplies with
 constexpr int W_RING_BYTES = 128 * 1024;
 
@@ -119,7 +124,7 @@ __device__ __forceinline__ float norm_weight(const void* w, int f32, int i) {
 
 // MT: 64-row units of the weight tile (BN = 64 MT rows; a warp owns 16 MT of them).
 template <int MT>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParams p) {
   constexpr int BN = 64 * MT;
   constexpr int STAGE_BYTES = BN * 128;
@@ -145,7 +150,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   const int k_lo = kb_lo * BK, kc = nkb * BK;                                  // this CTA's columns, padded to 64
   const int ldx = kc + 8;                                                      // padded row: conflict-free ldmatrix
 
-  if (threadIdx.x < STAGES) { mbar_init(full + threadIdx.x, 1); mbar_init(empty + threadIdx.x, WARPS); }
+  if (threadIdx.x < STAGES) { mbar_init(full + threadIdx.x, 1); mbar_init(empty + threadIdx.x, ROW_WARPS); }
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();
 
@@ -163,122 +168,156 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
       tma_load_2d(dst, &wmap, (kb_lo + j) * BK, w_row0, full + s);
     }
   };
-  // The weights do not depend on the prologue: start streaming them first.
-  if (threadIdx.x == 0)
-    for (int j = 0; j < STAGES - 1 && j < nkb; ++j) issue(j);
+  // The weights do not depend on the prologue: the feeding warp starts streaming them at once.
+  const bool feeder = warp == WARPS;
+  if (feeder && lane == 0)
+    for (int j = 0; j < STAGES && j < nkb; ++j) issue(j);
 
   // ---- prologue: the rows of x' for columns [k_lo, k_lo + kc) as bfloat16 in shared memory
+  constexpr int ALL_WARPS = WARPS + 1;
   if (p.residual != nullptr) {
-    for (int m = warp; m < M; m += WARPS) {
+    // Two warps share a row's sum of squares when there are rows to spare (8 rows, 17 warps): one row a warp.
+    for (int m = warp; m < M; m += ALL_WARPS) {
       const size_t src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K;
       float ss = 0.0f;
-      for (int k = lane * 8; k < K; k += 32 * 8) {                             // K is a multiple of 8 (checked by the launcher)
-        float a[8], b[8];
-        Vec16<bf16>::load(p.x + src + k, a);
-        Vec16<bf16>::load(p.residual + src + k, b);
+      for (int k0 = 0; k0 < K; k0 += 4 * 32 * 8) {                             // four 16-byte loads in flight per tensor
+        uint4 xa[4], xb[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { const float s = a[i] + b[i]; ss += s * s; }
+        for (int u = 0; u < 4; ++u) {
+          const int k = k0 + (u * 32 + lane) * 8;
+          xa[u] = xb[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (k < K) {
+            xa[u] = *reinterpret_cast<const uint4*>(p.x + src + k);
+            xb[u] = *reinterpret_cast<const uint4*>(p.residual + src + k);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t wa[4] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w}, wb[4] = {xb[u].x, xb[u].y, xb[u].z, xb[u].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float s0 = __uint_as_float(wa[i] << 16) + __uint_as_float(wb[i] << 16);
+            const float s1 = __uint_as_float(wa[i] & 0xffff0000u) + __uint_as_float(wb[i] & 0xffff0000u);
+            ss += s0 * s0 + s1 * s1;
+          }
+        }
       }
       ss = warp_sum(ss);
       if (lane == 0) row_scale[m] = rsqrtf(ss / static_cast<float>(K) + p.eps);
     }
     __syncthreads();
     const bool writer = blockIdx.x == 0 && p.residual_out != nullptr;
-    for (int m = warp; m < mpad; m += WARPS) {
-      const size_t src = m < M ? static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K : 0;
-      const float scale = m < M ? row_scale[m] : 0.0f;
-      // The writer CTA walks the whole row (it stores the new residual), the others only their columns.
-      const int k_begin = writer ? 0 : k_lo, k_end = writer ? max(K, k_lo + kc) : k_lo + kc;
-      for (int k = k_begin + lane * 8; k < k_end; k += 32 * 8) {
-        float a[8], b[8];
-        const bool live = m < M && k < K;
-        if (live) { Vec16<bf16>::load(p.x + src + k, a); Vec16<bf16>::load(p.residual + src + k, b); }
-        __align__(16) bf16 sum_rounded[8];
-        __align__(16) bf16 normed[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float s = live ? a[i] + b[i] : 0.0f;
-          sum_rounded[i] = __float2bfloat16_rn(s);
-          normed[i] = __float2bfloat16_rn(live ? s * scale * norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f);
-        }
-        if (writer && live) *reinterpret_cast<uint4*>(p.residual_out + src + k) = *reinterpret_cast<uint4*>(sum_rounded);
-        if (k >= k_lo && k < k_lo + kc) *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(normed);
+    // The writer CTA walks the whole row (it stores the new residual), the others only their columns.
+    const int k_begin = writer ? 0 : k_lo, k_end = writer ? max((K + 7) / 8 * 8, k_lo + kc) : k_lo + kc;
+    const int chunks = (k_end - k_begin) / 8;
+    for (int c = threadIdx.x; c < mpad * chunks; c += THREADS) {
+      const int m = c / chunks, k = k_begin + (c - m * chunks) * 8;
+      const bool live = m < M && k < K;
+      float a[8], b[8];
+      size_t src = 0;
+      float scale = 0.0f;
+      if (live) {
+        src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K;
+        scale = row_scale[m];
+        Vec16<bf16>::load(p.x + src + k, a);
+        Vec16<bf16>::load(p.residual + src + k, b);
       }
+      __align__(16) bf16 sum_rounded[8];
+      __align__(16) bf16 normed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float sum = live ? a[i] + b[i] : 0.0f;
+        sum_rounded[i] = __float2bfloat16_rn(sum);
+        normed[i] = __float2bfloat16_rn(live ? sum * scale * norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f);
+      }
+      if (writer && live) *reinterpret_cast<uint4*>(p.residual_out + src + k) = *reinterpret_cast<uint4*>(sum_rounded);
+      if (k >= k_lo && k < k_lo + kc) *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(normed);
     }
   } else {
-    for (int m = warp; m < mpad; m += WARPS) {
-      const size_t src = m < M ? static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K : 0;
-      for (int k = k_lo + lane * 8; k < k_lo + kc; k += 32 * 8) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (m < M && k < K) v = *reinterpret_cast<const uint4*>(p.x + src + k);
-        *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = v;
-      }
+    const int chunks = kc / 8;
+    for (int c = threadIdx.x; c < mpad * chunks; c += THREADS) {
+      const int m = c / chunks, k = k_lo + (c - m * chunks) * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (m < M && k < K) v = *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K + k);
+      *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = v;
     }
   }
   __syncthreads();
 
-  // ---- product: this warp's 16 MT weight rows against the rows of x'
+  // ---- product: group `grp` takes the k-blocks grp, grp + GROUPS, ...; inside a group warp `rw` owns 16 MT weight rows
   float acc[MT][2][4];
 #pragma unroll
   for (int i = 0; i < MT; ++i)
 #pragma unroll
     for (int n = 0; n < 2; ++n) { acc[i][n][0] = acc[i][n][1] = acc[i][n][2] = acc[i][n][3] = 0.0f; }
   const int mi = lane >> 3, r8 = lane & 7;
+  const int grp = warp / ROW_WARPS, rw = warp % ROW_WARPS;
   bool ok = true;
-  for (int it = 0; it < nkb; ++it) {
-    const int s = it % STAGES;
-    if (threadIdx.x == 0) {
-      const int j = it + STAGES - 1;
-      if (j < nkb) {
-        const int use = j / STAGES;
-        if (use > 0) ok = mbar_wait(empty + j % STAGES, (use - 1) & 1, p.err);
+  if (feeder) {
+    if (lane == 0) {
+      for (int j = STAGES; j < nkb && ok; ++j) {
+        ok = mbar_wait(empty + j % STAGES, (j / STAGES - 1) & 1, p.err);      // the group that had this stage has left it
         if (ok) issue(j);
       }
     }
-    if (!mbar_wait(full + s, (it / STAGES) & 1, p.err)) { ok = false; break; }
-    const unsigned char* wt = ring + s * STAGE_BYTES;
+  } else {
+    for (int it = grp; it < nkb; it += GROUPS) {
+      const int s = it % STAGES;
+      if (!mbar_wait(full + s, (it / STAGES) & 1, p.err)) { ok = false; break; }
+      const unsigned char* wt = ring + s * STAGE_BYTES;
 #pragma unroll
-    for (int ks = 0; ks < BK / 16; ++ks) {
-      // B operand: x'[m][k], two 8-row groups (m 0..7, 8..15), k and k + 8
-      uint32_t b[4];
-      // (with 8 rows of x' only, the lanes of the second group point at the first: its result is not used)
-      ldmatrix_x4(b, xs + ((mpad > 8 ? (mi >> 1) * 8 : 0) + r8) * ldx + it * BK + ks * 16 + (mi & 1) * 8);
+      for (int ks = 0; ks < BK / 16; ++ks) {
+        // B operand: x'[m][k], two 8-row groups (m 0..7, 8..15), k and k + 8
+        // (with 8 rows of x' only, the lanes of the second group point at the first: its result is not used)
+        uint32_t b[4];
+        ldmatrix_x4(b, xs + ((mpad > 8 ? (mi >> 1) * 8 : 0) + r8) * ldx + it * BK + ks * 16 + (mi & 1) * 8);
 #pragma unroll
-      for (int i = 0; i < MT; ++i) {
-        const int r = warp * (16 * MT) + i * 16 + (lane & 15);                 // weight row inside the tile
-        const int c = ks * 2 + (lane >> 4);                                    // 16-byte chunk of the 128-byte row
-        uint32_t a[4];
-        ldmatrix_x4(a, wt + r * 128 + ((c ^ (r & 7)) << 4));
-        mma_bf16(acc[i][0], a, b[0], b[1]);
-        if (mpad > 8) mma_bf16(acc[i][1], a, b[2], b[3]);
+        for (int i = 0; i < MT; ++i) {
+          const int r = rw * (16 * MT) + i * 16 + (lane & 15);                 // weight row inside the tile
+          const int c = ks * 2 + (lane >> 4);                                  // 16-byte chunk of the 128-byte row
+          uint32_t a[4];
+          ldmatrix_x4(a, wt + r * 128 + ((c ^ (r & 7)) << 4));
+          mma_bf16(acc[i][0], a, b[0], b[1]);
+          if (mpad > 8) mma_bf16(acc[i][1], a, b[2], b[3]);
+        }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + s);
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty + s);
   }
 
-  // ---- the partial sums of the cluster meet in rank 0, added in rank order
+  // ---- the groups' sums are added in shared memory, group after group
   const int g = lane >> 2, t2 = (lane & 3) * 2;
+  for (int turn = 0; turn < GROUPS; ++turn) {
+    if (!feeder && grp == turn) {
 #pragma unroll
-  for (int i = 0; i < MT; ++i) {
-    const int n = warp * (16 * MT) + i * 16 + g;
+      for (int i = 0; i < MT; ++i) {
+        const int n = rw * (16 * MT) + i * 16 + g;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int m = nt * 8 + t2;
-      if (m < mpad) {
-        red[m * (BN + 1) + n] = acc[i][nt][0];
-        red[(m + 1) * (BN + 1) + n] = acc[i][nt][1];
-        red[m * (BN + 1) + n + 8] = acc[i][nt][2];
-        red[(m + 1) * (BN + 1) + n + 8] = acc[i][nt][3];
+        for (int nt = 0; nt < 2; ++nt) {
+          const int m = nt * 8 + t2;
+          if (m < mpad) {
+            float* r0 = red + m * (BN + 1) + n;
+            float* r1 = red + (m + 1) * (BN + 1) + n;
+            if (turn == 0) { r0[0] = acc[i][nt][0]; r1[0] = acc[i][nt][1]; r0[8] = acc[i][nt][2]; r1[8] = acc[i][nt][3]; }
+            else { r0[0] += acc[i][nt][0]; r1[0] += acc[i][nt][1]; r0[8] += acc[i][nt][2]; r1[8] += acc[i][nt][3]; }
+          }
+        }
       }
     }
+    __syncthreads();
   }
+  // ---- the partial sums of the cluster meet in rank 0, added in rank order
   cluster.sync();
   if (rank == 0 && p.ksplit > 1) {
     for (int i = threadIdx.x; i < mpad * BN; i += blockDim.x) {
       const int m = i / BN, n = i - m * BN;
+      float part[8];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) part[r] = r < p.ksplit ? cluster.map_shared_rank(red, r)[m * (BN + 1) + n] : 0.0f;
       float sum = red[m * (BN + 1) + n];
-      for (int r = 1; r < p.ksplit; ++r) sum += cluster.map_shared_rank(red, r)[m * (BN + 1) + n];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) sum += part[r];
       red[m * (BN + 1) + n] = sum;
     }
   }
@@ -308,7 +347,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
     constexpr int d = BN;
     const int head = tile;
     const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
-    for (int m = warp; m < M; m += WARPS) {
+    for (int m = warp; m < M; m += WARPS + 1) {
       float* row = red + m * (BN + 1);
       // the projection's output is a bfloat16 tensor in the unfused path; the same rounding here
       for (int i = lane; i < d; i += 32) row[i] = __bfloat162float(__float2bfloat16_rn(row[i]));
@@ -412,9 +451,10 @@ static int choose_ksplit(int m, int n_tiles, int k, int sm_count) {
   const int kblocks = (k + BK - 1) / BK;
   int need = (k + kc_max - 1) / kc_max;
   if (need > 8) return 0;
-  // More CTAs while SMs are idle, as long as every CTA keeps at least four k-blocks.
+  // More CTAs while SMs are idle, as long as every CTA keeps at least sixteen k-blocks (128 KB of weights at
+  // 64 rows): below that the cluster's hand-over costs more than the idle SMs.
   int split = need;
-  while (split < 8 && n_tiles * split < sm_count && kblocks / (split * 2) >= 4) split *= 2;
+  while (split < 8 && n_tiles * split * 2 <= sm_count && kblocks / (split * 2) >= 16) split *= 2;
   if (split > 8) split = 8;
   return split < 1 ? 1 : split;
 }
@@ -434,7 +474,7 @@ static int launch(const CUtensorMap& map, const SkinnyParams& p, int n_tiles, cu
   }
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(n_tiles * p.ksplit);
-  config.blockDim = dim3(WARPS * 32);
+  config.blockDim = dim3(THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attr[1];
