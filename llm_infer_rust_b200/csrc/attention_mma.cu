@@ -241,6 +241,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
   bf16* qs = reinterpret_cast<bf16*>(tiles + static_cast<size_t>(WARPS) * STAGES * TILE_BYTES);   // [16][LD]
   uint64_t* bars = reinterpret_cast<uint64_t*>(qs + QROWS * LD);                                   // [WARPS][STAGES]
 
+  if (threadIdx.x < WARPS * STAGES) mbar_init(bars + threadIdx.x, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  pdl_launch_dependents();
+  pdl_wait();                      // the step's index arrays, q and the newest keys and values come from earlier kernels
   const int splits = gridDim.x, split = blockIdx.x, kvh = blockIdx.y;
   const int row = rows[blockIdx.z];
   const int group = nh / nkv, head0 = kvh * group;
@@ -261,8 +265,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (r < group) v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(tok) * nh + head0 + r) * D + part * 8);
     *reinterpret_cast<uint4*>(qs + r * LD + part * 8) = v;
   }
-  if (threadIdx.x < WARPS * STAGES) mbar_init(bars + threadIdx.x, 1);
-  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();
   const int g = lane >> 2;
   const int qpos0 = g < group ? qp : -1, qpos1 = g + 8 < group ? qp : -1;
@@ -363,6 +365,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
                                         const float* __restrict__ part_ml, const int* __restrict__ cu_q,
                                         const int* __restrict__ rows, int nh, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int head = blockIdx.y;
   const int tok = cu_q[rows[blockIdx.x]];
   const size_t base = (static_cast<size_t>(blockIdx.x) * nh + head) * splits;
@@ -596,15 +600,13 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
   float* part_acc = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
   dim3 grid(splits, nkv, n_rows);
-  decode_mma_kernel<kWarps, kStages><<<grid, kWarps * 32, smem, stream>>>(
-      kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table, table_stride,
-      cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
-  int rc = b200_check_launch();
+  int rc = b200_launch(decode_mma_kernel<kWarps, kStages>, grid, dim3(kWarps * 32), smem, stream, 0, kmap, vmap,
+                       static_cast<const bf16*>(q), static_cast<bf16*>(out), part_acc, part_ml, block_table, table_stride,
+                       cu_q, kv_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
   if (rc != 0 || splits == 1) return rc;
   dim3 mgrid(n_rows, nh);
-  decode_mma_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(static_cast<bf16*>(out), part_acc, part_ml, cu_q,
-                                                                    rows, nh, splits);
-  return b200_check_launch();
+  return b200_launch(decode_mma_merge_kernel, mgrid, dim3(D >= 128 ? 128 : 64), 0, stream, 0, static_cast<bf16*>(out),
+                     static_cast<const float*>(part_acc), static_cast<const float*>(part_ml), cu_q, rows, nh, splits);
 }
 
 constexpr size_t kPfQBytes = PF_ROWS * LD * sizeof(bf16);

@@ -91,7 +91,44 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
+// Programmatic dependent launch.  A kernel launched with b200_launch (below) may be scheduled while the kernel
+// before it in the stream is still running: what does not depend on that kernel (barrier set-up, fetching
+// weights) then overlaps its tail.  EVERY block of such a kernel calls pdl_wait() before it touches anything
+// the earlier kernel may have written, and before it exits: the wait returns when the earlier kernel has
+// finished and its writes are visible (at once, when the launch carried no such dependency).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+// Lets the kernel after this one be scheduled from now on (it still waits in its own pdl_wait()).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 static inline int b200_check_launch() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Launches `kernel` so that it may overlap the tail of the kernel before it (see pdl_wait), optionally as
+// clusters of `cluster_x` blocks.
+template <typename... KernelArgs, typename... Args>
+static inline int b200_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_x, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster_x > 0) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  config.attrs = attr;
+  config.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+  return e == cudaSuccess ? b200_check_launch() : static_cast<int>(e);
 }

@@ -172,6 +172,8 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   const bool feeder = warp == WARPS;
   if (feeder && lane == 0)
     for (int j = 0; j < STAGES && j < nkb; ++j) issue(j);
+  pdl_launch_dependents();
+  pdl_wait();                      // x, the residual and the cache belong to the kernels before this one
 
   // ---- prologue: the rows of x' for columns [k_lo, k_lo + kc) as bfloat16 in shared memory
   constexpr int ALL_WARPS = WARPS + 1;
@@ -472,20 +474,7 @@ static int launch(const CUtensorMap& map, const SkinnyParams& p, int n_tiles, cu
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(n_tiles * p.ksplit);
-  config.blockDim = dim3(THREADS);
-  config.dynamicSmemBytes = smem;
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = p.ksplit;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  config.attrs = attr;
-  config.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, skinny_linear_kernel<MT>, map, p);
-  return e == cudaSuccess ? b200_check_launch() : static_cast<int>(e);
+  return b200_launch(skinny_linear_kernel<MT>, dim3(n_tiles * p.ksplit), dim3(THREADS), smem, stream, p.ksplit, map, p);
 }
 
 // `params`: a SkinnyParams filled by the caller (ksplit is chosen here); `w_map`: the descriptor of the weight.
