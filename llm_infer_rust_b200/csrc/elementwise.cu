@@ -51,6 +51,53 @@ __global__ void rms_norm_kernel(TA* out, const TA* x, TA* residual, const TW* __
     dst[i] = from_f32<TA>(row_buf[i] * scale * to_f32<TW>(w[i]));
 }
 
+// Rows whose width is a multiple of the 16-byte vector and at most 32 * VPL vectors: one WARP per row, the row's
+// values stay in registers between the sum of squares and the scaling, loads and stores are 16 bytes wide.
+// The sum runs over the lanes' partial sums in a fixed order, so a row's result does not depend on other rows.
+template <typename TA, typename TW, bool ADD, int VPL>
+__global__ void __launch_bounds__(256)
+rms_norm_warp_kernel(TA* out, const TA* x, TA* residual, const TW* __restrict__ w, const int* __restrict__ rows,
+                     int n_rows, int width, float eps, int write_residual) {
+  constexpr int N = Vec16<TA>::N;
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const size_t src = static_cast<size_t>(rows ? rows[r] : r) * width;
+  const int vectors = width / N;
+  float v[VPL][N];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * N;
+    if (i * 32 + lane < vectors) {
+      Vec16<TA>::load(x + src + c, v[i]);
+      if (ADD) {
+        float b[N];
+        Vec16<TA>::load(residual + src + c, b);
+        __align__(16) TA rounded[N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) { v[i][e] += b[e]; rounded[e] = from_f32<TA>(v[i][e]); }
+        if (write_residual) *reinterpret_cast<uint4*>(residual + src + c) = *reinterpret_cast<const uint4*>(rounded);
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  ss = warp_sum(ss);
+  const float scale = rsqrtf(ss / static_cast<float>(width) + eps);
+  TA* dst = out + static_cast<size_t>(r) * width;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * N;
+    if (i * 32 + lane < vectors) {
+      __align__(16) TA y[N];
+#pragma unroll
+      for (int e = 0; e < N; ++e) y[e] = from_f32<TA>(v[i][e] * scale * to_f32<TW>(w[c + e]));
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(y);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ SwiGLU activation
 template <typename TA>
 __global__ void silu_mul_kernel(TA* __restrict__ out, const TA* __restrict__ gate_up, int width,
@@ -61,6 +108,25 @@ __global__ void silu_mul_kernel(TA* __restrict__ out, const TA* __restrict__ gat
     const float g = to_f32<TA>(gate_up[row * 2 * width + col]);
     const float u = to_f32<TA>(gate_up[row * 2 * width + width + col]);
     out[i] = from_f32<TA>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+// The same with 16-byte loads and stores: `width` is a multiple of the vector length and the pointers are aligned.
+template <typename TA>
+__global__ void silu_mul_vec_kernel(TA* __restrict__ out, const TA* __restrict__ gate_up, int width, size_t vectors) {
+  constexpr int N = Vec16<TA>::N;
+  const int per_row = width / N;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < vectors;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = i / per_row;
+    const int col = static_cast<int>(i - row * per_row) * N;
+    float g[N], u[N];
+    Vec16<TA>::load(gate_up + row * 2 * width + col, g);
+    Vec16<TA>::load(gate_up + row * 2 * width + width + col, u);
+    __align__(16) TA r[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) r[e] = from_f32<TA>(g[e] / (1.0f + expf(-g[e])) * u[e]);
+    *reinterpret_cast<uint4*>(out + row * width + col) = *reinterpret_cast<const uint4*>(r);
   }
 }
 
@@ -95,6 +161,27 @@ B200_EXPORT int b200_rms_norm(void* out, const void* x, void* residual, const vo
                               int w_dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (width <= 0) return B200_BAD_SIZE;
+  {
+    // The warp-per-row kernel where it applies (16-byte aligned rows of at most 32 * 4 vectors).
+    const int vec = act_dtype == B200_F32 ? 4 : 8;
+    const bool aligned = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(residual) % 16 == 0;
+    if (width % vec == 0 && width / vec <= 32 * 16 && aligned) {
+      const int blocks = (n_rows + 7) / 8;
+      const bool small = width / vec <= 32 * 4;
+#define LAUNCHW(TA, TW, ADD, VPL)                                                                            \
+      rms_norm_warp_kernel<TA, TW, ADD, VPL><<<blocks, 256, 0, stream>>>(static_cast<TA*>(out),               \
+          static_cast<const TA*>(x), static_cast<TA*>(residual), static_cast<const TW*>(w), rows, n_rows, width, eps, \
+          write_residual)
+#define CALLW(TA, TW)                                                                                        \
+      if (residual) { if (small) LAUNCHW(TA, TW, true, 4); else LAUNCHW(TA, TW, true, 16); }                 \
+      else { if (small) LAUNCHW(TA, TW, false, 4); else LAUNCHW(TA, TW, false, 16); }
+      DISPATCH2(act_dtype, w_dtype, CALLW)
+#undef CALLW
+#undef LAUNCHW
+      return b200_check_launch();
+    }
+  }
   const size_t smem = (static_cast<size_t>(width) + 33) * sizeof(float);
   if (smem > 200 * 1024) return B200_BAD_SIZE;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
@@ -121,6 +208,19 @@ B200_EXPORT int b200_silu_mul(void* out, const void* gate_up, int tokens, int wi
   if (tokens <= 0) return 0;
   if (width <= 0) return B200_BAD_SIZE;
   const size_t total = static_cast<size_t>(tokens) * width;
+  const int vec = act_dtype == B200_F32 ? 4 : 8;
+  if (width % vec == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0) {
+    const size_t vectors = total / vec;
+    const int vblocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (vectors + 255) / 256));
+    if (act_dtype == B200_F32)
+      silu_mul_vec_kernel<float><<<vblocks, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up),
+                                                              width, vectors);
+    else if (act_dtype == B200_BF16)
+      silu_mul_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>(
+          static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), width, vectors);
+    else return B200_BAD_DTYPE;
+    return b200_check_launch();
+  }
   const int blocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (total + 255) / 256));
   if (act_dtype == B200_F32)
     silu_mul_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(out),

@@ -93,6 +93,83 @@ __global__ void qkv_post_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_o
   }
 }
 
+// The same work with 16-byte accesses, for heads whose size is 16 bytes times a power of two of at most 32 (64,
+// 128 or 256 elements in bfloat16) and a rotation over the whole head: `lanes` = head_dim / vector length lanes
+// share one (token, head); the sum of squares is reduced and the rotation partner (element i <-> i + d/2) is
+// fetched with shuffles, nothing passes through shared memory.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+qkv_post_vec_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out, TA* __restrict__ k_cache,
+                    TA* __restrict__ v_cache, const TW* __restrict__ q_w, const TW* __restrict__ k_w, float eps,
+                    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_pos,
+                    const int* __restrict__ positions, const int* __restrict__ slots, int tokens, int nh, int nkv,
+                    int d, int page_size, long long cache_slots, int lanes, int* err) {
+  constexpr int N = Vec16<TA>::N;
+  const int heads = nh + 2 * nkv;
+  const int sub = threadIdx.x % lanes;                          // this lane's place inside its (token, head)
+  const long long work = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / lanes;
+  const bool live = work < static_cast<long long>(tokens) * heads;
+  const int t = live ? static_cast<int>(work / heads) : 0;
+  const int h = live ? static_cast<int>(work - static_cast<long long>(t) * heads) : 0;
+  const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+  float v[N];
+#pragma unroll
+  for (int e = 0; e < N; ++e) v[e] = 0.0f;
+  if (live) Vec16<TA>::load(qkv + (static_cast<size_t>(t) * heads + h) * d + sub * N, v);
+
+  TA* dst = nullptr;
+  if (live) {
+    if (is_q) {
+      dst = q_out + (static_cast<size_t>(t) * nh + h) * d;
+    } else if (slots != nullptr) {
+      const int slot = slots[t];
+      if (slot < 0 || slot >= cache_slots) {
+        if (sub == 0) atomicOr(err, B200_ERR_SLOT_RANGE);
+      } else if (slot != 0) {
+        const int kvh = is_k ? h - nh : h - nh - nkv;
+        const int page = slot / page_size, offset = slot - page * page_size;
+        dst = (is_k ? k_cache : v_cache) + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * d;
+      }
+    }
+  }
+  const unsigned full = 0xffffffffu;
+  // Every lane of the warp executes the shuffles (a warp may hold a key head beside a value head); only the
+  // lanes of q and k heads use their results.
+  float ss = 0.0f;
+#pragma unroll
+  for (int e = 0; e < N; ++e) ss += v[e] * v[e];
+  for (int o = lanes >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(full, ss, o, lanes);
+  const TW* w = is_q ? q_w : k_w;
+  if ((is_q || is_k) && w != nullptr) {
+    const float scale = rsqrtf(ss / static_cast<float>(d) + eps);
+#pragma unroll
+    for (int e = 0; e < N; ++e) v[e] = v[e] * scale * to_f32<TW>(w[sub * N + e]);
+  }
+  const int half_lanes = lanes >> 1;
+  float partner[N];
+#pragma unroll
+  for (int e = 0; e < N; ++e) partner[e] = __shfl_xor_sync(full, v[e], half_lanes, lanes);
+  if (cos_table != nullptr && (is_q || is_k) && live) {
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+      if (sub == 0) atomicOr(err, B200_ERR_POSITION_RANGE);
+    } else {
+      const bool first = sub < half_lanes;
+      const int ci = (first ? sub : sub - half_lanes) * N;
+      const float* c = cos_table + static_cast<size_t>(pos) * (d / 2) + ci;
+      const float* sn = sin_table + static_cast<size_t>(pos) * (d / 2) + ci;
+#pragma unroll
+      for (int e = 0; e < N; ++e) v[e] = first ? v[e] * c[e] - partner[e] * sn[e] : v[e] * c[e] + partner[e] * sn[e];
+    }
+  }
+  if (dst != nullptr) {
+    __align__(16) TA r[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) r[e] = from_f32<TA>(v[e]);
+    *reinterpret_cast<uint4*>(dst + sub * N) = *reinterpret_cast<const uint4*>(r);
+  }
+}
+
 B200_EXPORT int b200_qkv_post(const void* qkv, void* q_out, void* k_cache, void* v_cache, const void* q_w,
                               const void* k_w, float eps, const float* cos_table, const float* sin_table,
                               int rot_dim, int max_pos, const int* positions, const int* slots, int tokens,
@@ -102,6 +179,29 @@ B200_EXPORT int b200_qkv_post(const void* qkv, void* q_out, void* k_cache, void*
   if (d <= 0 || d > MAX_HEAD_DIM || nh <= 0 || nkv <= 0 || page_size <= 0) return B200_BAD_SIZE;
   if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return B200_BAD_SIZE;
   const long long work = static_cast<long long>(tokens) * (nh + 2 * nkv);
+  {
+    const int vec = act_dtype == B200_F32 ? 4 : 8;
+    const int lanes = d % vec == 0 ? d / vec : 0;
+    const bool aligned = reinterpret_cast<uintptr_t>(qkv) % 16 == 0 && reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0;
+    const bool whole_rotation = cos_table == nullptr || rot_dim == d;
+    if (lanes >= 2 && lanes <= 32 && (lanes & (lanes - 1)) == 0 && aligned && whole_rotation) {
+      const long long threads = work * lanes;
+      const unsigned vblocks = static_cast<unsigned>((threads + 255) / 256);
+#define CALLV(TA, TW)                                                                                          \
+      qkv_post_vec_kernel<TA, TW><<<vblocks, 256, 0, stream>>>(                                                 \
+          static_cast<const TA*>(qkv), static_cast<TA*>(q_out), static_cast<TA*>(k_cache), static_cast<TA*>(v_cache), \
+          static_cast<const TW*>(q_w), static_cast<const TW*>(k_w), eps, cos_table, sin_table, max_pos, positions, \
+          slots, tokens, nh, nkv, d, page_size, cache_slots, lanes, err)
+      if (act_dtype == B200_F32 && w_dtype == B200_F32) { CALLV(float, float); }
+      else if (act_dtype == B200_BF16 && w_dtype == B200_BF16) { CALLV(__nv_bfloat16, __nv_bfloat16); }
+      else if (act_dtype == B200_BF16 && w_dtype == B200_F32) { CALLV(__nv_bfloat16, float); }
+      else if (act_dtype == B200_F32 && w_dtype == B200_BF16) { CALLV(float, __nv_bfloat16); }
+      else return B200_BAD_DTYPE;
+#undef CALLV
+      return b200_check_launch();
+    }
+  }
   const unsigned blocks = static_cast<unsigned>((work + WARPS - 1) / WARPS);
 #define CALL(TA, TW)                                                                                   \
   qkv_post_kernel<TA, TW><<<blocks, WARPS * 32, 0, stream>>>(                                          \
