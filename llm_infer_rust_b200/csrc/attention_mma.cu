@@ -151,6 +151,8 @@ struct WarpAcc {
 
 // One block of 32 keys against the 16 query rows in `qs`.  `qpos0/1`: position of the query in rows
 // lane/4 and lane/4 + 8 (-1: the row is unused).  `scale_log2` = softmax scale * log2(e).
+// MASKED = false: the caller knows that every key of the block is visible to every used row of the warp.
+template <bool MASKED>
 __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* ks, const unsigned char* vs, int first_key, int kv_end,
                                           int window, int qpos0, int qpos1, float scale_log2, WarpAcc& st) {
   const int lane = threadIdx.x & 31;
@@ -176,10 +178,13 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
   for (int n = 0; n < 4; ++n) {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const int key = first_key + n * 8 + t2 + e;
-      const bool in_seq = key < kv_end;
-      const bool v0 = in_seq && qpos0 >= 0 && key <= qpos0 && (window <= 0 || key > qpos0 - window);
-      const bool v1 = in_seq && qpos1 >= 0 && key <= qpos1 && (window <= 0 || key > qpos1 - window);
+      bool v0 = qpos0 >= 0, v1 = qpos1 >= 0;
+      if (MASKED) {
+        const int key = first_key + n * 8 + t2 + e;
+        const bool in_seq = key < kv_end;
+        v0 = in_seq && v0 && key <= qpos0 && (window <= 0 || key > qpos0 - window);
+        v1 = in_seq && v1 && key <= qpos1 && (window <= 0 || key > qpos1 - window);
+      }
       s[n][e] = v0 ? s[n][e] * scale_log2 : -INFINITY;
       s[n][2 + e] = v1 ? s[n][2 + e] * scale_log2 : -INFINITY;
       mx0 = fmaxf(mx0, s[n][e]);
@@ -206,8 +211,10 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
   st.m[0] = m0; st.m[1] = m1;
   st.l[0] = st.l[0] * c0 + sum0;
   st.l[1] = st.l[1] * c1 + sum1;
+  if (__any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f)) {       // no row's maximum moved: nothing to rescale
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) { st.o[i][0] *= c0; st.o[i][1] *= c0; st.o[i][2] *= c1; st.o[i][3] *= c1; }
+    for (int i = 0; i < D / 8; ++i) { st.o[i][0] *= c0; st.o[i][1] *= c0; st.o[i][2] *= c1; st.o[i][3] *= c1; }
+  }
 #pragma unroll
   for (int kk = 0; kk < 2; ++kk) {
     uint32_t a[4];
@@ -310,7 +317,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
       for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
     }
     __syncwarp();
-    block_mma(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, scale_log2, st);
+    if (first_key + KB <= kv_end && (window <= 0 || first_key > qp - window))
+      block_mma<false>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, scale_log2, st);
+    else
+      block_mma<true>(qs, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos0, qpos1, scale_log2, st);
     __syncwarp();                                      // every lane is done reading before the stage is refilled
     if (++stage == STAGES) { stage = 0; parity ^= 1u; }
   }
@@ -501,8 +511,15 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
       for (int c = 0; c < NB * 8; ++c) *reinterpret_cast<uint4*>(t + NB * HALF_BYTES + (c >> 3) * HALF_BYTES + lane * 128 + (c & 7) * 16) = zero;
     }
     __syncwarp();
-    if (w_tok_hi >= w_tok_lo && first_key <= w_p_hi && first_key + KB > w_first_key)
-      block_mma(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], scale_log2, st);
+    if (w_tok_hi >= w_tok_lo && first_key <= w_p_hi && first_key + KB > w_first_key) {
+      // All keys of the block lie at or before the warp's first query (and inside its last query's window)?
+      const bool all_visible = first_key + KB - 1 <= p_lo + w_tok_lo && first_key + KB <= kv_end &&
+                               (window <= 0 || first_key > w_p_hi - window);
+      if (all_visible)
+        block_mma<false>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], scale_log2, st);
+      else
+        block_mma<true>(my_q, t, t + NB * HALF_BYTES, first_key, kv_end, window, qpos[0], qpos[1], scale_log2, st);
+    }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + s);
   }
