@@ -403,6 +403,8 @@ __global__ void decode_mma_merge_kernel(bf16* __restrict__ out, const float* __r
 // warp has finished with it.  Each query vector has its own position, so the causal mask (and the
 // window) is applied per row of the score tile.
 constexpr int PF_WARPS = 4;
+// Three CTAs share an SM for heads up to 128 wide (the register budget that this leaves is 170 a thread).
+constexpr int PF_MIN_CTAS = D <= 128 ? 3 : 1;
 constexpr int PF_ROWS = PF_WARPS * 16;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -410,7 +412,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 template <int STAGES>
-__global__ void __launch_bounds__(PF_WARPS * 32, 1)
+__global__ void __launch_bounds__(PF_WARPS * 32, PF_MIN_CTAS)
 prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                    const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
                    int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
@@ -428,7 +430,8 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
   const int tokens_per_warp = 16 / group;                       // whole tokens per warp
   const int tile_tokens = tokens_per_warp * PF_WARPS;
   const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
-  const int tok0 = blockIdx.x * tile_tokens;
+  // The last tiles of a row see the most keys: they start first, so that the short ones fill the tail.
+  const int tok0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * tile_tokens;
   if (tok0 >= q_len) return;
   const int ntok = min(tile_tokens, q_len - tok0);
   const int prefix = prefix_len[row];
@@ -628,7 +631,7 @@ B200_EXPORT int b200_decode_attention_mma(const void* q, const void* k_map, cons
 
 constexpr size_t kPfQBytes = PF_ROWS * LD * sizeof(bf16);
 constexpr size_t kPfFixed = 1024 + kPfQBytes + kBarBytes;
-constexpr int kPfStages = kPfFixed + 4 * TILE_BYTES <= kSmemLimit ? 4 : (kPfFixed + 3 * TILE_BYTES <= kSmemLimit ? 3 : 2);
+constexpr int kPfStages = D <= 128 ? 3 : kPfFixed + 4 * TILE_BYTES <= kSmemLimit ? 4 : (kPfFixed + 3 * TILE_BYTES <= kSmemLimit ? 3 : 2);
 static_assert(kPfFixed + kPfStages * TILE_BYTES <= kSmemLimit, "the key blocks must fit shared memory");
 
 // Portions of prompts over a bfloat16 cache; arguments as b200_prefill_attention of attention.cu, with the
