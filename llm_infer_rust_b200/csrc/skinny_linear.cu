@@ -4,7 +4,8 @@
 //   prologue  none, or residual add + RMSNorm: s = x + residual in float, residual_out = round(s),
 //             x' = s * rsqrt(mean(s^2) + eps) * w (the unrounded sum is normalised; reference:
 //             src/layers/fused_ops.cu:95-105).  Every CTA recomputes the row statistics (the rows are few
-//             and sit in L2); the CTA with index 0 writes residual_out.
+//             and sit in L2); the CTA with index 0 writes residual_out.  The row's scale is a scalar, so it is
+//             applied to the finished product: the operand in shared memory is round(s * w).
 //   product   W is [N, K] bfloat16, row-major.  A CTA owns BN = 64 * MT weight rows and a range of K; TMA
 //             brings boxes of BN rows x 64 columns (128-byte swizzle) into a ring of stages, the rows of
 //             x' (at most 16) wait in shared memory, and mma.sync m16n8k16 multiplies with the WEIGHT rows
@@ -178,11 +179,20 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   // ---- prologue: the rows of x' for columns [k_lo, k_lo + kc) as bfloat16 in shared memory
   constexpr int ALL_WARPS = WARPS + 1;
   if (p.residual != nullptr) {
-    // Two warps share a row's sum of squares when there are rows to spare (8 rows, 17 warps): one row a warp.
-    for (int m = warp; m < M; m += ALL_WARPS) {
+    // One warp per row, one pass: the sum s = x + residual is stored rounded (by the writer CTA), its squares
+    // are summed, and s * w goes to shared memory as bfloat16.  The row's scale rsqrt(mean(s^2) + eps) is a
+    // scalar, so it multiplies the finished product instead (in the epilogue): the weights' product need not
+    // wait for the statistics.
+    const bool writer = blockIdx.x == 0 && p.residual_out != nullptr;
+    const int k_pad = (K + 7) / 8 * 8;
+    for (int m = warp; m < mpad; m += ALL_WARPS) {
+      if (m >= M) {                                                            // padding rows of x' are zeros
+        for (int k = lane * 8; k < kc; k += 32 * 8) *reinterpret_cast<uint4*>(xs + m * ldx + k) = make_uint4(0u, 0u, 0u, 0u);
+        continue;
+      }
       const size_t src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K;
       float ss = 0.0f;
-      for (int k0 = 0; k0 < K; k0 += 4 * 32 * 8) {                             // four 16-byte loads in flight per tensor
+      for (int k0 = 0; k0 < max(k_pad, k_lo + kc); k0 += 4 * 32 * 8) {           // four 16-byte loads in flight per tensor
         uint4 xa[4], xb[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -195,45 +205,32 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
+          const int k = k0 + (u * 32 + lane) * 8;
           const uint32_t wa[4] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w}, wb[4] = {xb[u].x, xb[u].y, xb[u].z, xb[u].w};
+          float sum[8];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float s0 = __uint_as_float(wa[i] << 16) + __uint_as_float(wb[i] << 16);
-            const float s1 = __uint_as_float(wa[i] & 0xffff0000u) + __uint_as_float(wb[i] & 0xffff0000u);
-            ss += s0 * s0 + s1 * s1;
+            sum[2 * i] = __uint_as_float(wa[i] << 16) + __uint_as_float(wb[i] << 16);
+            sum[2 * i + 1] = __uint_as_float(wa[i] & 0xffff0000u) + __uint_as_float(wb[i] & 0xffff0000u);
+            ss += sum[2 * i] * sum[2 * i] + sum[2 * i + 1] * sum[2 * i + 1];
+          }
+          if (writer && k < K) {
+            __align__(16) bf16 rounded[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rounded[i] = __float2bfloat16_rn(sum[i]);
+            *reinterpret_cast<uint4*>(p.residual_out + src + k) = *reinterpret_cast<uint4*>(rounded);
+          }
+          if (k >= k_lo && k < k_lo + kc) {
+            __align__(16) bf16 weighted[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              weighted[i] = __float2bfloat16_rn(k < K ? sum[i] * norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f);
+            *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(weighted);
           }
         }
       }
       ss = warp_sum(ss);
       if (lane == 0) row_scale[m] = rsqrtf(ss / static_cast<float>(K) + p.eps);
-    }
-    __syncthreads();
-    const bool writer = blockIdx.x == 0 && p.residual_out != nullptr;
-    // The writer CTA walks the whole row (it stores the new residual), the others only their columns.
-    const int k_begin = writer ? 0 : k_lo, k_end = writer ? max((K + 7) / 8 * 8, k_lo + kc) : k_lo + kc;
-    const int chunks = (k_end - k_begin) / 8;
-    for (int c = threadIdx.x; c < mpad * chunks; c += THREADS) {
-      const int m = c / chunks, k = k_begin + (c - m * chunks) * 8;
-      const bool live = m < M && k < K;
-      float a[8], b[8];
-      size_t src = 0;
-      float scale = 0.0f;
-      if (live) {
-        src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K;
-        scale = row_scale[m];
-        Vec16<bf16>::load(p.x + src + k, a);
-        Vec16<bf16>::load(p.residual + src + k, b);
-      }
-      __align__(16) bf16 sum_rounded[8];
-      __align__(16) bf16 normed[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float sum = live ? a[i] + b[i] : 0.0f;
-        sum_rounded[i] = __float2bfloat16_rn(sum);
-        normed[i] = __float2bfloat16_rn(live ? sum * scale * norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f);
-      }
-      if (writer && live) *reinterpret_cast<uint4*>(p.residual_out + src + k) = *reinterpret_cast<uint4*>(sum_rounded);
-      if (k >= k_lo && k < k_lo + kc) *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(normed);
     }
   } else {
     const int chunks = kc / 8;
@@ -325,6 +322,13 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   }
   cluster.sync();                    // the others' shared memory has been read: they may leave
   if (rank != 0 || !ok) return;
+  if (p.residual != nullptr) {       // the norm's row scale, left out of x' by the prologue
+    for (int i = threadIdx.x; i < M * BN; i += blockDim.x) {
+      const int m = i / BN, n = i - m * BN;
+      red[m * (BN + 1) + n] *= row_scale[m];
+    }
+    __syncthreads();
+  }
 
   // ---- epilogue on red[m][n] (float)
   if (p.mode == EPI_PLAIN_BF16 || p.mode == EPI_PLAIN_F32) {
@@ -434,15 +438,16 @@ B200_EXPORT int b200_weight_tensor_map(void* out_map, const void* weight, long l
   return 0;
 }
 
-// Rows of the weight tile that a CTA owns in `mode` for head size `head_dim` (QKV only): 64, 128 or 256; 0: refused.
-B200_EXPORT int b200_skinny_tile_rows(int mode, int head_dim) {
-  if (mode != EPI_QKV) return 128;
-  return (head_dim == 64 || head_dim == 128 || head_dim == 256) ? head_dim : 0;
+// Rows of the weight tile that a CTA owns: QKV: the head size (64, 128 or 256; 0: refused); else 128.
+B200_EXPORT int b200_skinny_tile_rows(int mode, int head_dim, int n, int sm_count) {
+  (void)n; (void)sm_count;
+  if (mode == EPI_QKV) return (head_dim == 64 || head_dim == 128 || head_dim == 256) ? head_dim : 0;
+  return 128;
 }
 
-// Rows of a weight box that b200_weight_tensor_map must be given for `mode`.
-B200_EXPORT int b200_skinny_box_rows(int mode, int head_dim) {
-  const int bn = b200_skinny_tile_rows(mode, head_dim);
+// Rows of a weight box that b200_weight_tensor_map must be given.
+B200_EXPORT int b200_skinny_box_rows(int mode, int head_dim, int n, int sm_count) {
+  const int bn = b200_skinny_tile_rows(mode, head_dim, n, sm_count);
   return mode == EPI_SWIGLU ? bn / 2 : bn;
 }
 
@@ -487,7 +492,7 @@ B200_EXPORT int b200_skinny_linear(const void* w_map, const void* params, int he
   if (p.M > MMAX || p.N <= 0 || p.K <= 0 || p.K % 8 != 0) return B200_BAD_SIZE;
   if (p.mode < EPI_PLAIN_BF16 || p.mode > EPI_QKV) return B200_BAD_SIZE;
   if (p.mode == EPI_SWIGLU && p.N % 2 != 0) return B200_BAD_SIZE;
-  const int bn = b200_skinny_tile_rows(p.mode, head_dim);
+  const int bn = b200_skinny_tile_rows(p.mode, head_dim, p.N, sm_count);
   if (bn == 0) return B200_BAD_SIZE;
   if (p.mode == EPI_QKV && (p.N != (p.nh + 2 * p.nkv) * head_dim || p.rot_dim < 0 || p.rot_dim > head_dim || (p.rot_dim & 1)))
     return B200_BAD_SIZE;

@@ -150,11 +150,12 @@ def test_few_row_product_plain(m, n, k, with_norm):
             src = o.PendingNorm(x if gather else x[:m].contiguous(), res if gather else res[:m].contiguous(), nw, 1e-5,
                                 rows=rows if gather else None, write_residual=not gather)
             s_sum = x[sel].float() + res[sel].float()
-            xin = _bf(s_sum * torch.rsqrt((s_sum * s_sum).mean(-1, keepdim=True) + 1e-5) * nw.float())
+            # the kernel multiplies round(s * w) and applies the row's scale to the finished product
+            xin, row_scale = _bf(s_sum * nw.float()), torch.rsqrt((s_sum * s_sum).mean(-1, keepdim=True) + 1e-5)
         else:
             src = x if gather else x[:m].contiguous()
-            xin = x[sel].float()
-        want = xin @ w.float().t()
+            xin, row_scale = x[sel].float(), 1.0
+        want = (xin @ w.float().t()) * row_scale
         for mode, dtype in ((o.EPI_PLAIN_F32, torch.float32), (o.EPI_PLAIN_BF16, torch.bfloat16)):
             got = o.skinny_linear(src, w, mode, x_rows=rows if (gather and not with_norm) else None)
             assert got.dtype == dtype and tuple(got.shape) == (m, n)
@@ -205,14 +206,14 @@ def test_few_row_product_qkv(m, nh, nkv, d, k, with_norm):
     if with_norm:
         src = o.PendingNorm(x, res, nw, 1e-5)
         s_sum = x.float() + res.float()
-        xin = _bf(s_sum * torch.rsqrt((s_sum * s_sum).mean(-1, keepdim=True) + 1e-5) * nw.float())
+        xin, row_scale = _bf(s_sum * nw.float()), torch.rsqrt((s_sum * s_sum).mean(-1, keepdim=True) + 1e-5)
     else:
-        src, xin = x, x.float()
+        src, xin, row_scale = x, x.float(), 1.0
     out = o.skinny_linear(src, w, o.EPI_QKV, qkv=dict(head_dim=d, num_heads=nh, num_kv_heads=nkv, q_out=q, k_cache=kc,
                                                       v_cache=vc, q_weight=qw, k_weight=kw, eps=eps, cos=cos, sin=sin,
                                                       rot_dim=d, positions=positions, slots=slots))
     assert out is q
-    qkv = (xin @ w.float().t()).to(torch.bfloat16)
+    qkv = ((xin @ w.float().t()) * row_scale).to(torch.bfloat16)
     rq, rk, rv = R.ref_qkv_post(qkv, qw, kw, eps, cos, sin, d, positions, nh, nkv, d)
     want_k, want_v = torch.full_like(kc, 7.0), torch.full_like(vc, 7.0)
     R.ref_store_kv(want_k, want_v, rk, rv, slots)
