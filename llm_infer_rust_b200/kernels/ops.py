@@ -498,6 +498,62 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     return out
 
 
+# --------------------------------------------------------------------------- many-row products on tcgen05
+GEMM_PLAIN, GEMM_SWIGLU = 0, 1
+_gemm_maps = {}
+
+
+def _gemm_map(t: torch.Tensor):
+    key = (t.data_ptr(), tuple(t.shape))
+    buf = _gemm_maps.get(key)
+    if buf is None:
+        buf = ctypes.create_string_buffer(128)
+        rc = load_cuda_library("gemm_tcgen05.cu").b200_gemm_tensor_map(buf, _p(t), ctypes.c_longlong(t.shape[0]),
+                                                                       ctypes.c_longlong(t.shape[1]))
+        if rc != 0:
+            raise KernelError(f"the TMA descriptor of a matrix could not be made (code {rc})")
+        if len(_gemm_maps) > 8192:
+            _gemm_maps.clear()
+        _gemm_maps[key] = buf
+    return buf
+
+
+def gemm_tc_ok(x: torch.Tensor, weight: torch.Tensor, mode: int = GEMM_PLAIN) -> bool:
+    """bfloat16 row-major operands on the device, K a multiple of 8 (16-byte rows for TMA); SwiGLU: even N."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_cuda and weight.is_cuda
+            and x.dim() == 2 and weight.dim() == 2 and x.is_contiguous() and weight.is_contiguous()
+            and x.shape[1] == weight.shape[1] and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0 and (mode == GEMM_PLAIN or weight.shape[0] % 2 == 0))
+
+
+def gemm_tc_pays(x: torch.Tensor, weight: torch.Tensor, mode: int = GEMM_PLAIN) -> bool:
+    """Whether the tcgen05 product is the faster way: measured on B200, the fused SwiGLU form ties or beats the
+    library product followed by the activation kernel once every SM has several tiles of 128 x 256 and K is
+    long (1,369 against 1,354 TFLOP/s at 2,048 x 24,576 x 4,096); on smaller shapes the library is ahead."""
+    if mode != GEMM_SWIGLU or not gemm_tc_ok(x, weight, mode):
+        return False
+    tiles = -(-x.shape[0] // 128) * -(-(weight.shape[0] // 2) // 128)
+    return x.shape[1] >= 2048 and tiles >= 4 * _sm_count(x.device)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, mode: int = GEMM_PLAIN) -> torch.Tensor:
+    """x . weight^T on the tcgen05 tensor cores (TMA-fed, float sums in tensor memory), bfloat16 out.
+    ``GEMM_SWIGLU``: weight = [gate rows; up rows]; the result is silu(x . gate^T) * (x . up^T)."""
+    if not gemm_tc_ok(x, weight, mode):
+        raise KernelError("the tcgen05 product takes contiguous bfloat16 [M, K] and [N, K] with K a multiple of 8")
+    m, k = x.shape
+    n = weight.shape[0]
+    out = torch.empty((m, n // 2 if mode == GEMM_SWIGLU else n), dtype=torch.bfloat16, device=x.device)
+    a_map = ctypes.create_string_buffer(128)          # activations move: their descriptor is made per call
+    lib = load_cuda_library("gemm_tcgen05.cu")
+    rc = lib.b200_gemm_tensor_map(a_map, _p(x), ctypes.c_longlong(m), ctypes.c_longlong(k))
+    if rc != 0:
+        raise KernelError(f"the TMA descriptor of the activations could not be made (code {rc})")
+    rc = lib.b200_gemm_tcgen05(a_map, _gemm_map(weight), _p(out), m, n, k, mode, _p(error_word(x.device)), _stream())
+    _ok(rc, "gemm_tcgen05")
+    return out
+
+
 # --------------------------------------------------------------------------- matrix products
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a[M, K] . w[N, K]^T in true 32-bit on CUDA cores."""

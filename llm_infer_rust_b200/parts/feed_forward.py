@@ -33,6 +33,9 @@ class SwiGLU(Part):
             return ops.linear(ops.skinny_linear(x, self.params["gate_up_proj"], ops.EPI_SWIGLU), self.params["down_proj"])
         if isinstance(x, ops.PendingNorm):
             x = x.materialize()
+        if ops.gemm_tc_pays(x, self.params["gate_up_proj"], ops.GEMM_SWIGLU):
+            # many tokens, large matrices: gate and up projections with silu(gate) * up as the epilogue, on tcgen05
+            return ops.linear(ops.gemm_tc(x, self.params["gate_up_proj"], ops.GEMM_SWIGLU), self.params["down_proj"])
         gate_up = ops.linear(x, self.params["gate_up_proj"])
         return ops.linear(ops.silu_mul(gate_up), self.params["down_proj"])
 

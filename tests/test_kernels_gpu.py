@@ -235,6 +235,41 @@ def test_few_row_product_refusals():
         o.skinny_linear(rnd(17, 64, dtype=torch.bfloat16), w)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 1024), (200, 304, 96), (1, 8, 8), (1000, 1000, 1000),
+                                   (2048, 1024, 3072)])
+def test_tcgen05_product(m, n, k):
+    """The TMA-fed tcgen05 product (float sums in tensor memory) against a float reference: single and many
+    tiles and k-blocks, more tiles than SMs (the persistent loop and both accumulators), tails in M, N and K."""
+    o = ops()
+    x, w = rnd(m, k, dtype=torch.bfloat16, scale=0.5), rnd(n, k, dtype=torch.bfloat16, seed=1, scale=0.1)
+    got = o.gemm_tc(x, w)
+    want = x.float() @ w.float().t()
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (m, n)
+    assert (got.float() - want).abs().max() <= 2.0 ** -8 * max(1.0, float(want.abs().max()))     # one bfloat16 rounding
+    o.check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("m,inter,k", [(130, 256, 1024), (77, 100, 72), (2048, 3072, 1024), (300, 20000, 64)])
+def test_tcgen05_product_with_swiglu_epilogue(m, inter, k):
+    o = ops()
+    x, w = rnd(m, k, dtype=torch.bfloat16, scale=0.5), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.1)
+    got = o.gemm_tc(x, w, o.GEMM_SWIGLU)
+    gu = (x.float() @ w.float().t()).to(torch.bfloat16)
+    want = R.ref_silu_mul(gu).float()
+    assert tuple(got.shape) == (m, inter)
+    # gate and up are rounded to bfloat16 from sums in another order than the reference's: one ulp of each
+    assert (got.float() - want).abs().max() <= 2.0 ** -6 * max(1.0, float(want.abs().max()))
+    o.check_errors(torch.device(DEV))
+
+
+def test_tcgen05_product_refusals():
+    o = ops()
+    assert not o.gemm_tc_ok(rnd(4, 60, dtype=torch.bfloat16), rnd(8, 60, dtype=torch.bfloat16))      # K no multiple of 8
+    assert not o.gemm_tc_ok(rnd(4, 64), rnd(8, 64))                                                  # float32
+    with pytest.raises(o.KernelError, match="tcgen05"):
+        o.gemm_tc(rnd(4, 64), rnd(8, 64))
+
+
 QKV_CASES = [  # nh, nkv, d, rot, eps, with_norm
     (4, 2, 16, 16, 1e-6, True), (6, 2, 32, 32, 1e-5, True), (5, 5, 48, 48, 3e-6, True),
     (8, 1, 128, 128, 1e-6, True), (3, 3, 80, 32, 1e-6, True), (2, 1, 64, 64, 1e-6, False),
