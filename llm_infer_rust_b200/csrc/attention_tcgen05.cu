@@ -1,0 +1,377 @@
+// Causal prefill attention over the paged bfloat16 cache on the fifth-generation tensor cores, head size 128.
+//
+// A CTA serves 128 query vectors: 128 / group consecutive tokens of one row x the `group` query heads of one KV
+// head (row r of the tile = token r / group, head r mod group).  It walks the visible keys in blocks of 128:
+//   S = Q K^T      tcgen05.mma, M 128, N 128 (keys), K 16 x 8; Q and K are K-major tiles in the 128-byte swizzle
+//                  (Q is written there by the softmax warps, K arrives by TMA); S lands in tensor memory;
+//   softmax        four warps, one thread per query row: two passes over the row of S in tensor memory
+//                  (tcgen05.ld): the row maximum, then exp2 and the row sum; the probabilities go to shared
+//                  memory as a bfloat16 K-major tile (the A operand of the next product);
+//   O_blk = P V    tcgen05.mma, M 128, N 128 (head dims), K 16 x 8; V is used as it lies in the cache (keys x
+//                  dims, the dims contiguous: an MN-major B operand); O_blk lands in tensor memory and every
+//                  thread folds its row into float registers: O = O * exp2(m_old - m_new) + O_blk.
+// One warp (one lane issuing) fetches K and V blocks through a ring of two stages; one warp owns tensor memory
+// and issues the MMAs.  Semantics as attention.cu (reference: src/models/attention/backend.rs:1455-1498): causal
+// mask, optional window, scale as a parameter, softmax in float.  Value rows at or beyond what the tile may see are
+// zeroed in shared memory before they are used.  Every wait is bounded by the clock; on a time-out the error word
+// is flagged and every path still reaches the end, where tensor memory is given back.
+#include <cuda.h>
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+static_assert(HEAD_DIM == 128, "the tcgen05 attention kernel is written for head size 128");
+
+typedef __nv_bfloat16 bf16;
+constexpr int D = 128;
+constexpr int BQ = 128;                  // query vectors per CTA
+constexpr int BKV = 128;                 // keys per block
+constexpr int HALF = BKV * 128;          // bytes of a [128 rows x 64 columns] half tile
+constexpr int TILE = 2 * HALF;           // bytes of a [128 x 128] bfloat16 tile
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;             // warp 0: copies, warp 1: MMA, warps 2-5: softmax
+constexpr int TMEM_COLS = 256;           // S: columns 0..127, O_blk: columns 128..255
+
+// Shared memory: V stages, K stages, Q, P (each tile 32 KB), then the barriers.
+constexpr int V_OFF = 0, K_OFF = KV_STAGES * TILE, Q_OFF = 2 * KV_STAGES * TILE, P_OFF = Q_OFF + TILE, BAR_OFF = P_OFF + TILE;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t start = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (global_ns() - start > 1000000000ull) {
+      atomicOr(err, B200_ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// K-major tile in the 128-byte swizzle: 8-row groups 1024 bytes apart, leading byte offset unused (1).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+// MN-major tile in the 128-byte swizzle (rows = k, 64 MN elements = 128 bytes contiguous): 8-row groups 1024 bytes
+// apart (stride byte offset), the next 64 MN elements HALF bytes further (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (static_cast<uint32_t>(HALF >> 4) << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+// float accumulator, bfloat16 operands, M 128, N 128; B is K-major for S = Q K^T and MN-major for P V.
+constexpr uint32_t kDescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kDescPV = kDescQK | (1u << 16);
+
+__device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// Byte offset of (row r, 16-byte chunk c of 16) inside a [128 x 128] bfloat16 tile of two swizzled halves.
+__device__ __forceinline__ int swz(int r, int c) { return (c >> 3) * HALF + r * 128 + (((c & 7) ^ (r & 7)) << 4); }
+
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                       const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
+                       int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                       const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv, int page_size,
+                       int box_rows, int window, float scale_log2, int* err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(sm + BAR_OFF);     // [2]
+  uint64_t* kv_empty = kv_full + KV_STAGES;                          // [2]
+  uint64_t* q_full = kv_empty + KV_STAGES;
+  uint64_t* s_full = q_full + 1;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* o_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
+    mbar_init(q_full, 4);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();                                  // q, the step's index arrays and the newest keys and values come from earlier kernels
+
+  const int row = rows[blockIdx.z];
+  const int kvh = blockIdx.y;
+  const int group = nh / nkv, head0 = kvh * group;
+  const int tile_tokens = BQ / group;
+  const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
+  // The last tiles of a row see the most keys: they start first.
+  const int tok0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * tile_tokens;
+  const bool active = tok0 < q_len;            // (an idle CTA still walks to the end, where tensor memory is freed)
+  const int ntok = active ? min(tile_tokens, q_len - tok0) : 0;
+  const int prefix = prefix_len[row];
+  const int kv_end = active ? min(kv_len[row], prefix + tok0 + ntok) : 0;
+  const int p_lo = prefix + tok0;
+  int k_begin = window > 0 ? max(0, p_lo - window + 1) : 0;
+  k_begin -= k_begin % BKV;
+  const int nblk = active ? (kv_end - k_begin + BKV - 1) / BKV : 0;
+  const int* table = block_table + static_cast<size_t>(row) * table_stride;
+
+  if (warp == 0) {
+    // ---- copies: lane j fetches the sub-blocks j, j + 32, ... (box_rows keys each) of a block of 128 keys
+    bool ok = true;
+    for (int i = 0; i < nblk && ok; ++i) {
+      const int s = i % KV_STAGES, use = i / KV_STAGES;
+      if (use > 0) ok = mbar_wait(kv_empty + s, (use - 1) & 1, err);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;
+      if (!ok) break;
+      const int first_key = k_begin + i * BKV;
+      const int n_sub = (min(BKV, kv_end - first_key) + box_rows - 1) / box_rows;
+      proxy_fence();
+      if (lane == 0) mbar_expect_tx(kv_full + s, static_cast<uint32_t>(n_sub) * 4u * box_rows * 128u);
+      __syncwarp();
+      for (int j = lane; j < n_sub; j += 32) {
+        const int key0 = first_key + j * box_rows;
+        const int page = table[key0 / page_size];
+        const int y = (page * nkv + kvh) * page_size + key0 % page_size;
+        unsigned char* kd = sm + K_OFF + s * TILE + j * box_rows * 128;
+        unsigned char* vd = sm + V_OFF + s * TILE + j * box_rows * 128;
+        tma_load_2d(kd, &kmap, 0, y, kv_full + s);
+        tma_load_2d(kd + HALF, &kmap, 64, y, kv_full + s);
+        tma_load_2d(vd, &vmap, 0, y, kv_full + s);
+        tma_load_2d(vd + HALF, &vmap, 64, y, kv_full + s);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue (one lane): S_0; then for every block: P V of block i, S of block i + 1
+    if (lane == 0 && nblk > 0) {
+      bool ok = mbar_wait(q_full, 0, err);
+      const uint32_t q_addr = smem_u32(sm + Q_OFF), p_addr = smem_u32(sm + P_OFF);
+      const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+      auto issue_s = [&](int i) {
+        const int s = i % KV_STAGES;
+        if (!mbar_wait(kv_full + s, (i / KV_STAGES) & 1, err)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sm + K_OFF + s * TILE);
+#pragma unroll
+        for (int j = 0; j < D / 16; ++j) {
+          const uint32_t off = (j >> 2) * HALF + (j & 3) * 32;
+          umma(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), kDescQK, j > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int i = 0; i < nblk && ok; ++i) {
+        const int s = i % KV_STAGES;
+        ok = mbar_wait(p_full, i & 1, err);            // P of block i is in shared memory, S and O_blk have been read
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sm + V_OFF + s * TILE);
+#pragma unroll
+        for (int j = 0; j < BKV / 16; ++j)
+          umma(tmem_o, desc_k_major(p_addr + (j >> 2) * HALF + (j & 3) * 32), desc_mn_major(v_addr + j * 16 * 128), kDescPV,
+               j > 0 ? 1u : 0u);
+        umma_commit(o_full);
+        umma_commit(kv_empty + s);
+        if (i + 1 < nblk) ok = issue_s(i + 1);
+      }
+    }
+  } else {
+    // ---- softmax warps: thread t owns query row t of the tile (tensor-memory lane t)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int tok = r / group, head = head0 + r % group;
+    const bool used = tok < ntok;
+    const int qpos = used ? p_lo + tok : -1;
+    if (nblk > 0) {
+      // Q row into its swizzled K-major tile (zeros for an unused row)
+      const bf16* src = q + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (used) v = *reinterpret_cast<const uint4*>(src + c * 8);
+        *reinterpret_cast<uint4*>(sm + Q_OFF + swz(r, c)) = v;
+      }
+      proxy_fence();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_full);
+    }
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    bool ok = true;
+    for (int i = 0; i < nblk; ++i) {
+      const int s = i % KV_STAGES;
+      const int first_key = k_begin + i * BKV;
+      if (!mbar_wait(s_full, i & 1, err)) { ok = false; break; }
+      tc_fence_after();
+      // pass 1: the row's maximum over the block's visible keys
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_base + c * 32, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int key = first_key + c * 32 + e;
+          const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+          mx = fmaxf(mx, vis ? v[e] * scale_log2 : -INFINITY);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = m_new == -INFINITY ? 1.0f : exp2f(m_run - m_new);
+      const float base = m_new == -INFINITY ? 0.0f : m_new;
+      // pass 2: probabilities, their sum, and the bfloat16 tile P
+      float sum = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_base + c * 32, v);
+        __align__(16) bf16 pr[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int key = first_key + c * 32 + e;
+          const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+          const float pv = vis ? exp2f(v[e] * scale_log2 - base) : 0.0f;
+          sum += pv;
+          pr[e] = __float2bfloat16_rn(pv);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          *reinterpret_cast<uint4*>(sm + P_OFF + swz(r, c * 4 + q4)) = *reinterpret_cast<const uint4*>(pr + q4 * 8);
+      }
+      // value rows beyond what the tile may see must not reach P V, whatever the page or the stage held
+      if (first_key + BKV > kv_end && first_key + r >= kv_end) {
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
+      }
+      l_run = l_run * corr + sum;
+      m_run = m_new;
+      proxy_fence();                                   // P (and the zeroed rows) are visible to the tensor cores
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      // O = O * corr + P V
+      if (!mbar_wait(o_full, i & 1, err)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_base + 128 + c * 32, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * corr + v[e];
+      }
+      tc_fence_before();
+    }
+    if (ok && used) {
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        __align__(16) bf16 y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[c * 8 + e] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(y);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+B200_EXPORT int b200_attention_tcgen05_head_dim() { return D; }
+
+// Portions of prompts over a bfloat16 cache, head size 128; the number of query heads per KV head must divide 128
+// and the page size must be a power of two.  `k_map`, `v_map`: descriptors of b200_kv_tensor_map (attention_mma.cu)
+// with box_rows = min(page_size, 32).  Other arguments as b200_prefill_attention of attention.cu.
+B200_EXPORT int b200_prefill_attention_tcgen05(const void* q, const void* k_map, const void* v_map, void* out,
+                                               const int* block_table, int table_stride, const int* cu_q,
+                                               const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
+                                               int max_q_len, int nh, int nkv, int page_size, int window, float scale,
+                                               int* err, cudaStream_t stream) {
+  if (n_rows <= 0 || max_q_len <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || (page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
+  const int group = nh / nkv;
+  if (group > BQ || BQ % group != 0) return B200_BAD_SIZE;
+  const int box_rows = page_size < 32 ? page_size : 32;
+  const int tile_tokens = BQ / group;
+  const size_t smem = 1024 + BAR_OFF + 16 * sizeof(uint64_t);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  CUtensorMap kmap, vmap;
+  memcpy(&kmap, k_map, sizeof(kmap));
+  memcpy(&vmap, v_map, sizeof(vmap));
+  dim3 grid((max_q_len + tile_tokens - 1) / tile_tokens, nkv, n_rows);
+  return b200_launch(prefill_tcgen05_kernel, grid, dim3(THREADS), smem, stream, 0, kmap, vmap, static_cast<const bf16*>(q),
+                     static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size,
+                     box_rows, window, scale * 1.4426950408889634f, err);
+}

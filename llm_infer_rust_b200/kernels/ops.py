@@ -233,6 +233,15 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
         if k_cache.shape[1] != num_kv_heads or k_cache.shape[2] != page_size:
             raise KernelError("the cache must be [pages + 1, kv_heads, page_size, head_dim]")
         box_rows = min(page_size, 32)
+        group = num_heads // num_kv_heads
+        if head_dim == 128 and 128 % group == 0 and max_q_len * group >= 128:
+            # head size 128 and at least one full tile of 128 query vectors: the tcgen05 kernel
+            rc = load_cuda_library("attention_tcgen05.cu").b200_prefill_attention_tcgen05(
+                _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
+                block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
+                num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), _p(error_word(q.device)), _stream())
+            _ok(rc, "prefill_attention_tcgen05")
+            return
         rc = _attention_mma(head_dim).b200_prefill_attention_mma(
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
             block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
