@@ -3,15 +3,18 @@
 // A CTA serves 128 query vectors: 128 / group consecutive tokens of one row x the `group` query heads of one KV
 // head (row r of the tile = token r / group, head r mod group).  It walks the visible keys in blocks of 128:
 //   S = Q K^T      tcgen05.mma, M 128, N 128 (keys), K 16 x 8; Q and K are K-major tiles in the 128-byte swizzle
-//                  (Q is written there by the softmax warps, K arrives by TMA); S lands in tensor memory;
+//                  (Q is written there by the softmax warps, K arrives by TMA); S lands in one of TWO score
+//                  buffers in tensor memory, so the scores of block i + 1 are computed under the softmax of block i;
 //   softmax        four warps, one thread per query row: two passes over the row of S in tensor memory
 //                  (tcgen05.ld): the row maximum, then exp2 and the row sum; the probabilities go to shared
 //                  memory as a bfloat16 K-major tile (the A operand of the next product);
-//   O_blk = P V    tcgen05.mma, M 128, N 128 (head dims), K 16 x 8; V is used as it lies in the cache (keys x
-//                  dims, the dims contiguous: an MN-major B operand); O_blk lands in tensor memory and every
-//                  thread folds its row into float registers: O = O * exp2(m_old - m_new) + O_blk.
-// One warp (one lane issuing) fetches K and V blocks through a ring of two stages; one warp owns tensor memory
-// and issues the MMAs.  Semantics as attention.cu (reference: src/models/attention/backend.rs:1455-1498): causal
+//   O += P V       tcgen05.mma, M 128, N 128 (head dims), K 16 x 8, accumulating in tensor memory over all
+//                  blocks; V is used as it lies in the cache (keys x dims, the dims contiguous: an MN-major B
+//                  operand).  The probabilities are taken relative to a reference maximum that is raised only when
+//                  a row's maximum has grown by more than 2^8 (then that warp rescales its rows of O in tensor
+//                  memory: tcgen05.ld / st); a stale reference is exact, since the row sum uses the same one.
+// One warp fetches K blocks (ring of three) and V blocks (ring of two) by TMA; one warp owns tensor memory and
+// issues the MMAs.  Semantics as attention.cu (reference: src/models/attention/backend.rs:1455-1498): causal
 // mask, optional window, scale as a parameter, softmax in float.  Value rows at or beyond what the tile may see are
 // zeroed in shared memory before they are used.  Every wait is bounded by the clock; on a time-out the error word
 // is flagged and every path still reaches the end, where tensor memory is given back.
@@ -32,12 +35,13 @@ constexpr int BQ = 128;                  // query vectors per CTA
 constexpr int BKV = 128;                 // keys per block
 constexpr int HALF = BKV * 128;          // bytes of a [128 rows x 64 columns] half tile
 constexpr int TILE = 2 * HALF;           // bytes of a [128 x 128] bfloat16 tile
-constexpr int KV_STAGES = 2;
+constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int THREADS = 192;             // warp 0: copies, warp 1: MMA, warps 2-5: softmax
-constexpr int TMEM_COLS = 256;           // S: columns 0..127, O_blk: columns 128..255
+constexpr int TMEM_COLS = 512;           // S buffers: columns 0..127 and 128..255, O: columns 256..383
+constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only growth beyond 2^8
 
 // Shared memory: V stages, K stages, Q, P (each tile 32 KB), then the barriers.
-constexpr int V_OFF = 0, K_OFF = KV_STAGES * TILE, Q_OFF = 2 * KV_STAGES * TILE, P_OFF = Q_OFF + TILE, BAR_OFF = P_OFF + TILE;
+constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, P_OFF = Q_OFF + TILE, BAR_OFF = P_OFF + TILE;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -70,6 +74,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     }
   }
   return true;
+}
+// All lanes of a warp wait and agree on the outcome: the collective tensor-memory loads that follow need the
+// warp whole, also when a wait has run out.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* err) {
+  const bool mine = mbar_wait(bar, parity, err);
+  return __all_sync(0xffffffffu, mine ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -114,8 +124,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+               "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+               ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                 "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                 "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                 "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                 "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                 "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                 "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                 "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+               : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {      // 2^x, one special-function instruction (-inf gives 0)
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 // Byte offset of (row r, 16-byte chunk c of 16) inside a [128 x 128] bfloat16 tile of two swizzled halves.
@@ -129,21 +159,25 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        int box_rows, int window, float scale_log2, int* err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(sm + BAR_OFF);     // [2]
-  uint64_t* kv_empty = kv_full + KV_STAGES;                          // [2]
-  uint64_t* q_full = kv_empty + KV_STAGES;
-  uint64_t* s_full = q_full + 1;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* o_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(sm + BAR_OFF);      // [3]
+  uint64_t* k_empty = k_full + K_STAGES;                             // [3]
+  uint64_t* v_full = k_empty + K_STAGES;                             // [2]
+  uint64_t* v_empty = v_full + V_STAGES;                             // [2]
+  uint64_t* s_full = v_empty + V_STAGES;                             // [2]
+  uint64_t* q_full = s_full + 2;
+  uint64_t* p_full = q_full + 1;
+  uint64_t* pv_done = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-    mbar_init(q_full, 4);
+    for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+    for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
     mbar_init(s_full, 1);
+    mbar_init(s_full + 1, 1);
+    mbar_init(q_full, 4);
     mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
+    mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -175,63 +209,76 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int* table = block_table + static_cast<size_t>(row) * table_stride;
 
   if (warp == 0) {
-    // ---- copies: lane j fetches the sub-blocks j, j + 32, ... (box_rows keys each) of a block of 128 keys
+    // ---- copies: lane j fetches the sub-blocks j, j + 32, ... (box_rows keys each) of a block of 128 keys.
+    // Keys run one block further ahead than values (three stages against two): S of block i + 2 is wanted
+    // while block i is still in the softmax.
     bool ok = true;
-    for (int i = 0; i < nblk && ok; ++i) {
-      const int s = i % KV_STAGES, use = i / KV_STAGES;
-      if (use > 0) ok = mbar_wait(kv_empty + s, (use - 1) & 1, err);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;
-      if (!ok) break;
-      const int first_key = k_begin + i * BKV;
+    auto fetch = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int first_key) {
       const int n_sub = (min(BKV, kv_end - first_key) + box_rows - 1) / box_rows;
       proxy_fence();
-      if (lane == 0) mbar_expect_tx(kv_full + s, static_cast<uint32_t>(n_sub) * 4u * box_rows * 128u);
+      if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * box_rows * 128u);
       __syncwarp();
       for (int j = lane; j < n_sub; j += 32) {
         const int key0 = first_key + j * box_rows;
         const int page = table[key0 / page_size];
         const int y = (page * nkv + kvh) * page_size + key0 % page_size;
-        unsigned char* kd = sm + K_OFF + s * TILE + j * box_rows * 128;
-        unsigned char* vd = sm + V_OFF + s * TILE + j * box_rows * 128;
-        tma_load_2d(kd, &kmap, 0, y, kv_full + s);
-        tma_load_2d(kd + HALF, &kmap, 64, y, kv_full + s);
-        tma_load_2d(vd, &vmap, 0, y, kv_full + s);
-        tma_load_2d(vd + HALF, &vmap, 64, y, kv_full + s);
+        tma_load_2d(dst + j * box_rows * 128, map, 0, y, bar);
+        tma_load_2d(dst + HALF + j * box_rows * 128, map, 64, y, bar);
       }
+    };
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {        // every lane waits, then the warp agrees
+      const bool mine = mbar_wait(bar, parity, err);
+      return __all_sync(0xffffffffu, mine ? 1 : 0) != 0;
+    };
+    int ik = 0;                                                  // next key block to fetch
+    for (int i = 0; i < nblk && ok; ++i) {
+      for (; ik < nblk && ik <= i + K_STAGES - 1 && ok; ++ik) {
+        const int s = ik % K_STAGES, use = ik / K_STAGES;
+        if (use > 0) ok = wait_all(k_empty + s, (use - 1) & 1);
+        if (ok) fetch(&kmap, sm + K_OFF + s * TILE, k_full + s, k_begin + ik * BKV);
+      }
+      if (!ok) break;
+      const int s = i % V_STAGES, use = i / V_STAGES;
+      if (use > 0) ok = wait_all(v_empty + s, (use - 1) & 1);
+      if (ok) fetch(&vmap, sm + V_OFF + s * TILE, v_full + s, k_begin + i * BKV);
     }
   } else if (warp == 1) {
-    // ---- MMA issue (one lane): S_0; then for every block: P V of block i, S of block i + 1
+    // ---- MMA issue (one lane): S_0, S_1; then for every block: O += P V of block i, S of block i + 2
     if (lane == 0 && nblk > 0) {
       bool ok = mbar_wait(q_full, 0, err);
       const uint32_t q_addr = smem_u32(sm + Q_OFF), p_addr = smem_u32(sm + P_OFF);
-      const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+      const uint32_t tmem_o = tmem_base + 256;
       auto issue_s = [&](int i) {
-        const int s = i % KV_STAGES;
-        if (!mbar_wait(kv_full + s, (i / KV_STAGES) & 1, err)) return false;
+        const int s = i % K_STAGES;
+        if (!mbar_wait(k_full + s, (i / K_STAGES) & 1, err)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sm + K_OFF + s * TILE);
+        const uint32_t tmem_s = tmem_base + (i & 1) * 128;
 #pragma unroll
         for (int j = 0; j < D / 16; ++j) {
           const uint32_t off = (j >> 2) * HALF + (j & 3) * 32;
           umma(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), kDescQK, j > 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
+        umma_commit(s_full + (i & 1));
+        umma_commit(k_empty + s);
         return true;
       };
       if (ok) ok = issue_s(0);
+      if (ok && nblk > 1) ok = issue_s(1);
       for (int i = 0; i < nblk && ok; ++i) {
-        const int s = i % KV_STAGES;
-        ok = mbar_wait(p_full, i & 1, err);            // P of block i is in shared memory, S and O_blk have been read
+        const int s = i % V_STAGES;
+        ok = mbar_wait(p_full, i & 1, err);            // P of block i is in shared memory; S of block i has been read
+        if (ok) ok = mbar_wait(v_full + s, (i / V_STAGES) & 1, err);
         if (!ok) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sm + V_OFF + s * TILE);
 #pragma unroll
         for (int j = 0; j < BKV / 16; ++j)
           umma(tmem_o, desc_k_major(p_addr + (j >> 2) * HALF + (j & 3) * 32), desc_mn_major(v_addr + j * 16 * 128), kDescPV,
-               j > 0 ? 1u : 0u);
-        umma_commit(o_full);
-        umma_commit(kv_empty + s);
-        if (i + 1 < nblk) ok = issue_s(i + 1);
+               (i > 0 || j > 0) ? 1u : 0u);
+        umma_commit(pv_done);
+        umma_commit(v_empty + s);
+        if (i + 2 < nblk) ok = issue_s(i + 2);
       }
     }
   } else {
@@ -254,86 +301,119 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
     }
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
+    float m_ref = -INFINITY, l_run = 0.0f;             // reference maximum (log2 units) and the row sum relative to it
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
     for (int i = 0; i < nblk; ++i) {
-      const int s = i % KV_STAGES;
       const int first_key = k_begin + i * BKV;
-      if (!mbar_wait(s_full, i & 1, err)) { ok = false; break; }
+      const uint32_t s_base = lane_base + (i & 1) * 128;
+      if (!mbar_wait_warp(s_full + (i & 1), (i >> 1) & 1, err)) { ok = false; break; }
       tc_fence_after();
-      // pass 1: the row's maximum over the block's visible keys
+      const bool masked = first_key + BKV - 1 > p_lo || first_key + BKV > kv_end || (window > 0 && first_key <= p_lo + ntok - 1 - window);
+      // pass 1: the row's maximum over the block's visible keys (of the raw scores; the scale is positive)
       float mx = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float v[32];
-        tmem_ld32(lane_base + c * 32, v);
+        tmem_ld32(s_base + c * 32, v);
+        if (masked) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = first_key + c * 32 + e;
-          const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
-          mx = fmaxf(mx, vis ? v[e] * scale_log2 : -INFINITY);
+          for (int e = 0; e < 32; ++e) {
+            const int key = first_key + c * 32 + e;
+            const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+            mx = fmaxf(mx, vis ? v[e] : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, v[e]);
         }
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float corr = m_new == -INFINITY ? 1.0f : exp2f(m_run - m_new);
-      const float base = m_new == -INFINITY ? 0.0f : m_new;
-      // pass 2: probabilities, their sum, and the bfloat16 tile P
+      mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
+      // The reference follows the maximum when it grew by more than the step (or there was none yet).
+      const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
+      const float m_new = raise ? mx : m_ref;
+      const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
+      // P's buffer and (for a rescale) O are free when P V of the block before has finished.
+      if (i > 0 && !mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
+      tc_fence_after();
+      if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float v[32];
+          tmem_ld32(lane_base + 256 + c * 32, v);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] *= corr;
+          tmem_st32(lane_base + 256 + c * 32, v);
+        }
+      }
+      l_run *= corr;
+      m_ref = m_new;
+      const float base = m_ref == -INFINITY ? 0.0f : m_ref;
+      // pass 2: probabilities relative to the reference, their sum, and the bfloat16 tile P
       float sum = 0.0f;
+      const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float v[32];
-        tmem_ld32(lane_base + c * 32, v);
-        __align__(16) bf16 pr[32];
+        tmem_ld32(s_base + c * 32, v);
+        uint32_t pr[16];
+        if (masked) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = first_key + c * 32 + e;
-          const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
-          const float pv = vis ? exp2f(v[e] * scale_log2 - base) : 0.0f;
-          sum += pv;
-          pr[e] = __float2bfloat16_rn(pv);
+          for (int e = 0; e < 32; ++e) {
+            const int key = first_key + c * 32 + e;
+            const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+            v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          sum += v[e] + v[e + 1];
+          __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
+          pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
         }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<uint4*>(sm + P_OFF + swz(r, c * 4 + q4)) = *reinterpret_cast<const uint4*>(pr + q4 * 8);
+          *reinterpret_cast<uint4*>(sm + P_OFF + swz(r, c * 4 + q4)) = make_uint4(pr[q4 * 4], pr[q4 * 4 + 1], pr[q4 * 4 + 2], pr[q4 * 4 + 3]);
       }
+      l_run += sum;
       // value rows beyond what the tile may see must not reach P V, whatever the page or the stage held
-      if (first_key + BKV > kv_end && first_key + r >= kv_end) {
-        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+      if (first_key + BKV > kv_end) {
+        const int s = i % V_STAGES;
+        if (!mbar_wait_warp(v_full + s, (i / V_STAGES) & 1, err)) { ok = false; break; }      // the copies have landed
+        if (first_key + r >= kv_end) {
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
+          for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
+        }
       }
-      l_run = l_run * corr + sum;
-      m_run = m_new;
       proxy_fence();                                   // P (and the zeroed rows) are visible to the tensor cores
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      // O = O * corr + P V
-      if (!mbar_wait(o_full, i & 1, err)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(lane_base + 128 + c * 32, v);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] = o[c * 32 + e] * corr + v[e];
-      }
-      tc_fence_before();
     }
-    if (ok && used) {
+    if (ok && nblk > 0) ok = mbar_wait_warp(pv_done, (nblk - 1) & 1, err);
+    if (ok && nblk > 0) {
+      tc_fence_after();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_base + 256 + c * 32, v);        // (every lane of the warp takes part in the load)
+        if (used) {
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        __align__(16) bf16 y[8];
+          for (int q4 = 0; q4 < 4; ++q4) {
+            __align__(16) bf16 y[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[c * 8 + e] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(y);
+            for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(v[q4 * 8 + e] * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = *reinterpret_cast<const uint4*>(y);
+          }
+        }
       }
+      tc_fence_before();
     }
   }
   tc_fence_before();
