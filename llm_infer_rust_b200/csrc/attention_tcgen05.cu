@@ -124,6 +124,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 64 consecutive columns of this thread's lane, in one load and one wait.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n"
+               "tcgen05.wait::ld.sync.aligned;\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+               : "r"(taddr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -313,19 +323,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       // pass 1: the row's maximum over the block's visible keys (of the raw scores; the scale is positive)
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(s_base + c * 32, v);
+      for (int c = 0; c < 2; ++c) {
+        float v[64];
+        tmem_ld64(s_base + c * 64, v);
         if (masked) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = first_key + c * 32 + e;
+          for (int e = 0; e < 64; ++e) {
+            const int key = first_key + c * 64 + e;
             const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
             mx = fmaxf(mx, vis ? v[e] : -INFINITY);
           }
         } else {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, v[e]);
+          for (int e = 0; e < 64; e += 4) {
+            m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
+          }
+          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
         }
       }
       mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
@@ -333,7 +347,37 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
       const float m_new = raise ? mx : m_ref;
       const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
-      // P's buffer and (for a rescale) O are free when P V of the block before has finished.
+      const float base = m_new == -INFINITY ? 0.0f : m_new;
+      // pass 2: probabilities relative to the reference, their sum, and the bfloat16 tile P
+      float sum = 0.0f;
+      const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t pr[64];                                   // the row's 128 probabilities, packed
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[64];
+        tmem_ld64(s_base + c * 64, v);
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int key = first_key + c * 64 + e;
+            const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+            v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
+        }
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          sum4[(e >> 1) & 3] += v[e] + v[e + 1];
+          __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
+          pr[c * 32 + (e >> 1)] = *reinterpret_cast<uint32_t*>(&two);
+        }
+      }
+      sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // P's buffer and (for a rescale) O are free when P V of the block before has finished: the arithmetic above
+      // ran under that product, only the stores wait for it.
       if (i > 0 && !mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
       tc_fence_after();
       if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
@@ -346,38 +390,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
           tmem_st32(lane_base + 256 + c * 32, v);
         }
       }
-      l_run *= corr;
+      l_run = l_run * corr;
       m_ref = m_new;
-      const float base = m_ref == -INFINITY ? 0.0f : m_ref;
-      // pass 2: probabilities relative to the reference, their sum, and the bfloat16 tile P
-      float sum = 0.0f;
-      const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(s_base + c * 32, v);
-        uint32_t pr[16];
-        if (masked) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = first_key + c * 32 + e;
-            const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
-            v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
-        }
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          sum += v[e] + v[e + 1];
-          __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
-          pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<uint4*>(sm + P_OFF + swz(r, c * 4 + q4)) = make_uint4(pr[q4 * 4], pr[q4 * 4 + 1], pr[q4 * 4 + 2], pr[q4 * 4 + 3]);
-      }
+      for (int c16 = 0; c16 < 16; ++c16)
+        *reinterpret_cast<uint4*>(sm + P_OFF + swz(r, c16)) = make_uint4(pr[c16 * 4], pr[c16 * 4 + 1], pr[c16 * 4 + 2], pr[c16 * 4 + 3]);
       l_run += sum;
       // value rows beyond what the tile may see must not reach P V, whatever the page or the stage held
       if (first_key + BKV > kv_end) {
