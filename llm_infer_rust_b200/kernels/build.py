@@ -178,7 +178,7 @@ def load_cuda_library(source: str, defines: Optional[Dict[str, object]] = None) 
 
 def all_cuda_libraries(head_dims: Iterable[int]) -> List[tuple]:
     """(source, defines) of every CUDA library that the package can ask for, attention for ``head_dims``."""
-    per_head = ("attention.cu", "decode_attention_static.cu")
+    per_head = ("attention.cu", "attention_mma.cu", "decode_attention_static.cu")
     libs = [(f, None) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu") and f not in per_head]
     return libs + [(f, {"HEAD_DIM": int(d)}) for f in per_head for d in head_dims]
 
