@@ -60,6 +60,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {      // 2^x in one special-function instruction (-inf gives 0)
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -202,8 +207,8 @@ __device__ __forceinline__ void block_mma(const bf16* qs, const unsigned char* k
   for (int n = 0; n < 4; ++n) {
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      s[n][e] = exp2f(s[n][e] - base0);              // a masked score is -inf: exp2 gives 0
-      s[n][2 + e] = exp2f(s[n][2 + e] - base1);
+      s[n][e] = fast_exp2(s[n][e] - base0);          // a masked score is -inf: exp2 gives 0
+      s[n][2 + e] = fast_exp2(s[n][2 + e] - base1);
       sum0 += s[n][e];
       sum1 += s[n][2 + e];
     }
