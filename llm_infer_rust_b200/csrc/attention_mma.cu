@@ -429,15 +429,17 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_consta
   uint64_t* full = reinterpret_cast<uint64_t*>(qs + PF_ROWS * LD);
   uint64_t* empty = full + STAGES;
 
-  const int row = rows[blockIdx.z];
-  const int kvh = blockIdx.y;
+  // Grid: x = KV head, y = row, z = tile order.  CTAs start in the order x, y, z, and a row's last tiles see the
+  // most keys: every row's heaviest tiles start first, over all heads, so that the short ones fill the tail.
+  const int row = rows[blockIdx.y];
+  const int kvh = blockIdx.x;
   const int group = nh / nkv, head0 = kvh * group;
   const int tokens_per_warp = 16 / group;                       // whole tokens per warp
   const int tile_tokens = tokens_per_warp * PF_WARPS;
   const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
-  // The last tiles of a row see the most keys: they start first, so that the short ones fill the tail.
-  const int tok0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * tile_tokens;
-  if (tok0 >= q_len) return;
+  const int tile = (q_len + tile_tokens - 1) / tile_tokens - 1 - static_cast<int>(blockIdx.z);
+  if (tile < 0) return;
+  const int tok0 = tile * tile_tokens;
   const int ntok = min(tile_tokens, q_len - tok0);
   const int prefix = prefix_len[row];
   const int kv_end = min(kv_len[row], prefix + tok0 + ntok);     // causal: nothing later is visible to this tile
@@ -662,7 +664,9 @@ B200_EXPORT int b200_prefill_attention_mma(const void* q, const void* k_map, con
   CUtensorMap kmap, vmap;
   memcpy(&kmap, k_map, sizeof(kmap));
   memcpy(&vmap, v_map, sizeof(vmap));
-  dim3 grid((max_q_len + tile_tokens - 1) / tile_tokens, nkv, n_rows);
+  const int n_tiles = (max_q_len + tile_tokens - 1) / tile_tokens;
+  if (n_rows > 65535 || n_tiles > 65535) return B200_BAD_SIZE;      // the grid's y and z extents
+  dim3 grid(nkv, n_rows, n_tiles);
   prefill_mma_kernel<kPfStages><<<grid, PF_WARPS * 32, smem, stream>>>(
       kmap, vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
       prefix_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);

@@ -6,11 +6,13 @@
 //                  (Q is written there by the softmax warps, K arrives by TMA); S lands in one of TWO score
 //                  buffers in tensor memory, so the scores of block i + 1 are computed under the softmax of block i;
 //   softmax        four warps, one thread per query row: two passes over the row of S in tensor memory
-//                  (tcgen05.ld): the row maximum, then exp2 and the row sum; the probabilities go to shared
-//                  memory as a bfloat16 K-major tile (the A operand of the next product);
-//   O += P V       tcgen05.mma, M 128, N 128 (head dims), K 16 x 8, accumulating in tensor memory over all
-//                  blocks; V is used as it lies in the cache (keys x dims, the dims contiguous: an MN-major B
-//                  operand).  The probabilities are taken relative to a reference maximum that is raised only when
+//                  (tcgen05.ld): the row maximum, then exp2 and the row sum; the bfloat16 probabilities go back
+//                  into tensor memory (tcgen05.st), two to a column, over the first half of the scores they
+//                  came from;
+//   O += P V       tcgen05.mma with the A operand in tensor memory, M 128, N 128 (head dims), K 16 x 8,
+//                  accumulating in tensor memory over all blocks; V is used as it lies in the cache (keys x dims,
+//                  the dims contiguous: an MN-major B operand).  The tensor pipe runs the MMAs of one thread in
+//                  the order of issue, so the scores of block i + 2 overwrite the buffer only behind P V of block i.  The probabilities are taken relative to a reference maximum that is raised only when
 //                  a row's maximum has grown by more than 2^8 (then that warp rescales its rows of O in tensor
 //                  memory: tcgen05.ld / st); a stale reference is exact, since the row sum uses the same one.
 // One warp fetches K blocks (ring of three) and V blocks (ring of two) by TMA; one warp owns tensor memory and
@@ -37,11 +39,11 @@ constexpr int HALF = BKV * 128;          // bytes of a [128 rows x 64 columns] h
 constexpr int TILE = 2 * HALF;           // bytes of a [128 x 128] bfloat16 tile
 constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int THREADS = 192;             // warp 0: copies, warp 1: MMA, warps 2-5: softmax
-constexpr int TMEM_COLS = 512;           // S buffers: columns 0..127 and 128..255, O: columns 256..383
+constexpr int TMEM_COLS = 512;           // S buffers (and P in their first 64 columns): columns 0..127 and 128..255; O: 256..383
 constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only growth beyond 2^8
 
-// Shared memory: V stages, K stages, Q, P (each tile 32 KB), then the barriers.
-constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, P_OFF = Q_OFF + TILE, BAR_OFF = P_OFF + TILE;
+// Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers.
+constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, BAR_OFF = Q_OFF + TILE;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -107,6 +109,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t desc_a, uint64_t 
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The A operand from tensor memory: 16-bit elements packed two to a column (k = 2c, 2c + 1 in column c of lane m).
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -149,6 +157,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
                : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
+// 32 columns of this thread's lane from 32 registers; the caller waits (tcgen05.wait::st) before it tells anyone.
+__device__ __forceinline__ void tmem_st32_raw(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+               "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                 "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                 "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {      // 2^x, one special-function instruction (-inf gives 0)
@@ -201,14 +221,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   pdl_launch_dependents();
   pdl_wait();                                  // q, the step's index arrays and the newest keys and values come from earlier kernels
 
-  const int row = rows[blockIdx.z];
-  const int kvh = blockIdx.y;
+  // Grid: x = KV head, y = row, z = tile order.  CTAs start in the order x, y, z, and a row's last tiles see the
+  // most keys: every row's heaviest tiles start first, over all heads, and the light ones fill the gaps behind them.
+  const int row = rows[blockIdx.y];
+  const int kvh = blockIdx.x;
   const int group = nh / nkv, head0 = kvh * group;
   const int tile_tokens = BQ / group;
   const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
-  // The last tiles of a row see the most keys: they start first.
-  const int tok0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * tile_tokens;
-  const bool active = tok0 < q_len;            // (an idle CTA still walks to the end, where tensor memory is freed)
+  const int tile = (q_len + tile_tokens - 1) / tile_tokens - 1 - static_cast<int>(blockIdx.z);
+  const bool active = tile >= 0;               // (an idle CTA still walks to the end, where tensor memory is freed)
+  const int tok0 = active ? tile * tile_tokens : 0;
   const int ntok = active ? min(tile_tokens, q_len - tok0) : 0;
   const int prefix = prefix_len[row];
   const int kv_end = active ? min(kv_len[row], prefix + tok0 + ntok) : 0;
@@ -256,7 +278,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     // ---- MMA issue (one lane): S_0, S_1; then for every block: O += P V of block i, S of block i + 2
     if (lane == 0 && nblk > 0) {
       bool ok = mbar_wait(q_full, 0, err);
-      const uint32_t q_addr = smem_u32(sm + Q_OFF), p_addr = smem_u32(sm + P_OFF);
+      const uint32_t q_addr = smem_u32(sm + Q_OFF);
       const uint32_t tmem_o = tmem_base + 256;
       auto issue_s = [&](int i) {
         const int s = i % K_STAGES;
@@ -277,15 +299,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       if (ok && nblk > 1) ok = issue_s(1);
       for (int i = 0; i < nblk && ok; ++i) {
         const int s = i % V_STAGES;
-        ok = mbar_wait(p_full, i & 1, err);            // P of block i is in shared memory; S of block i has been read
+        ok = mbar_wait(p_full, i & 1, err);            // P of block i lies where S of block i lay
         if (ok) ok = mbar_wait(v_full + s, (i / V_STAGES) & 1, err);
         if (!ok) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sm + V_OFF + s * TILE);
 #pragma unroll
         for (int j = 0; j < BKV / 16; ++j)
-          umma(tmem_o, desc_k_major(p_addr + (j >> 2) * HALF + (j & 3) * 32), desc_mn_major(v_addr + j * 16 * 128), kDescPV,
-               (i > 0 || j > 0) ? 1u : 0u);
+          umma_a_tmem(tmem_o, tmem_base + (i & 1) * 128 + j * 8, desc_mn_major(v_addr + j * 16 * 128), kDescPV,
+                      (i > 0 || j > 0) ? 1u : 0u);
         umma_commit(pv_done);
         umma_commit(v_empty + s);
         if (i + 2 < nblk) ok = issue_s(i + 2);
@@ -348,12 +370,28 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       const float m_new = raise ? mx : m_ref;
       const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
       const float base = m_new == -INFINITY ? 0.0f : m_new;
-      // pass 2: probabilities relative to the reference, their sum, and the bfloat16 tile P
-      float sum = 0.0f;
+      // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
+      if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
+        if (!mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float v[32];
+          tmem_ld32(lane_base + 256 + c * 32, v);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] *= corr;
+          tmem_st32(lane_base + 256 + c * 32, v);
+        }
+      }
+      l_run = l_run * corr;
+      m_ref = m_new;
+      // pass 2: probabilities relative to the reference and their sum.  The bfloat16 probabilities of columns
+      // 64c .. 64c + 63 go back into tensor memory, two to a column, over the scores that were just read (columns
+      // 32c .. 32c + 31 of this score buffer): the A operand of P V.  The buffer's next scores are issued behind
+      // that product.
       const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      uint32_t pr[64];                                   // the row's 128 probabilities, packed
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         float v[64];
         tmem_ld64(s_base + c * 64, v);
@@ -368,34 +406,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
 #pragma unroll
           for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
         }
+        uint32_t pr[32];
 #pragma unroll
         for (int e = 0; e < 64; e += 2) {
           sum4[(e >> 1) & 3] += v[e] + v[e + 1];
           __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
-          pr[c * 32 + (e >> 1)] = *reinterpret_cast<uint32_t*>(&two);
+          pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
         }
+        tmem_st32_raw(s_base + c * 32, pr);
       }
-      sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // P's buffer and (for a rescale) O are free when P V of the block before has finished: the arithmetic above
-      // ran under that product, only the stores wait for it.
-      if (i > 0 && !mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
-      tc_fence_after();
-      if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          tmem_ld32(lane_base + 256 + c * 32, v);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] *= corr;
-          tmem_st32(lane_base + 256 + c * 32, v);
-        }
-      }
-      l_run = l_run * corr;
-      m_ref = m_new;
-#pragma unroll
-      for (int c16 = 0; c16 < 16; ++c16)
-        *reinterpret_cast<uint4*>(sm + P_OFF + swz(r, c16)) = make_uint4(pr[c16 * 4], pr[c16 * 4 + 1], pr[c16 * 4 + 2], pr[c16 * 4 + 3]);
-      l_run += sum;
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // value rows beyond what the tile may see must not reach P V, whatever the page or the stage held
       if (first_key + BKV > kv_end) {
         const int s = i % V_STAGES;
@@ -405,8 +425,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
 #pragma unroll
           for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
         }
+        proxy_fence();                                 // the zeroed rows are visible to the tensor cores
       }
-      proxy_fence();                                   // P (and the zeroed rows) are visible to the tensor cores
+      tmem_wait_st();                                  // P is in tensor memory
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
@@ -467,7 +488,9 @@ B200_EXPORT int b200_prefill_attention_tcgen05(const void* q, const void* k_map,
   CUtensorMap kmap, vmap;
   memcpy(&kmap, k_map, sizeof(kmap));
   memcpy(&vmap, v_map, sizeof(vmap));
-  dim3 grid((max_q_len + tile_tokens - 1) / tile_tokens, nkv, n_rows);
+  const int n_tiles = (max_q_len + tile_tokens - 1) / tile_tokens;
+  if (n_rows > 65535 || n_tiles > 65535) return B200_BAD_SIZE;      // the grid's y and z extents
+  dim3 grid(nkv, n_rows, n_tiles);
   return b200_launch(prefill_tcgen05_kernel, grid, dim3(THREADS), smem, stream, 0, kmap, vmap, static_cast<const bf16*>(q),
                      static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size,
                      box_rows, window, scale * 1.4426950408889634f, err);

@@ -405,6 +405,29 @@ def test_decode_attention(dtype, nh, nkv, d, page, window, splits):
     assert (out[6:] == 9.0).all()
 
 
+@pytest.mark.parametrize("nh,nkv,window", [(16, 8, None), (8, 1, None), (4, 4, 200), (32, 8, 77)])
+def test_prefill_attention_over_many_key_blocks(nh, nkv, window):
+    """Head size 128, rows that span up to nine blocks of 128 keys, prefixes that are no multiple of a block, and
+    one stretch of keys four times as large as the rest: the running maximum jumps there (the output accumulated
+    so far is rescaled) and falls back behind it (the probabilities stay relative to the old maximum)."""
+    o = ops()
+    d, page = 128, 16
+    rows = [(0, 700), (300, 333), (1000, 130), (5, 1), (0, 128)]
+    c = paged_case(rows, nh, nkv, d, page, torch.bfloat16, seed=7)
+    for r, (p, n) in enumerate(rows):
+        for pos in range(512, min(640, p + n)):
+            c["kc"][c["table"][r, pos // page], :, pos % page] *= 4.0
+    scale = 1.5 / math.sqrt(d)
+    out = torch.full_like(c["q"], 9.0)
+    serve = torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32, device=DEV)
+    o.prefill_attention(c["q"], c["kc"], c["vc"], out, c["table"], c["cu"], c["kv_len"], c["prefix"], serve, 5,
+                        700, nh, nkv, d, page, window, scale)
+    o.check_errors(torch.device(DEV))
+    want = R.ref_paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["kv_len"], c["prefix"], nh, nkv,
+                                 d, page, window, scale)
+    close(out, want, torch.bfloat16, bf16_atol=attention_atol(c))
+
+
 def test_attention_finds_one_far_key_among_a_thousand():
     """One key far back scores high: whoever skips or misplaces it changes the result."""
     o = ops()
