@@ -5,16 +5,18 @@
 //   S = Q K^T      tcgen05.mma, M 128, N 128 (keys), K 16 x 8; Q and K are K-major tiles in the 128-byte swizzle
 //                  (Q is written there by the softmax warps, K arrives by TMA); S lands in one of TWO score
 //                  buffers in tensor memory, so the scores of block i + 1 are computed under the softmax of block i;
-//   softmax        four warps, one thread per query row: two passes over the row of S in tensor memory
-//                  (tcgen05.ld): the row maximum, then exp2 and the row sum; the bfloat16 probabilities go back
-//                  into tensor memory (tcgen05.st), two to a column, over the first half of the scores they
-//                  came from;
+//   softmax        eight warps, two threads per query row with 64 keys each: the scores come into registers once
+//                  (tcgen05.ld), the two threads exchange their maxima through shared memory, then exp2 and the
+//                  row sum; the bfloat16 probabilities go back into tensor memory (tcgen05.st), two to a column,
+//                  over the first half of the scores they came from;
 //   O += P V       tcgen05.mma with the A operand in tensor memory, M 128, N 128 (head dims), K 16 x 8,
 //                  accumulating in tensor memory over all blocks; V is used as it lies in the cache (keys x dims,
 //                  the dims contiguous: an MN-major B operand).  The tensor pipe runs the MMAs of one thread in
-//                  the order of issue, so the scores of block i + 2 overwrite the buffer only behind P V of block i.  The probabilities are taken relative to a reference maximum that is raised only when
-//                  a row's maximum has grown by more than 2^8 (then that warp rescales its rows of O in tensor
-//                  memory: tcgen05.ld / st); a stale reference is exact, since the row sum uses the same one.
+//                  the order of issue, so the scores of block i + 2 overwrite the buffer only behind P V of block i.
+//                  The probabilities are taken relative to a reference maximum that is raised only when a row's
+//                  maximum has grown by more than 2^8 (then the row's two threads rescale its O in tensor memory,
+//                  tcgen05.ld / st, once P V of the block before is finished); a stale reference is exact, since
+//                  the row sum uses the same one.
 // One warp fetches K blocks (ring of three) and V blocks (ring of two) by TMA; one warp owns tensor memory and
 // issues the MMAs.  Semantics as attention.cu (reference: src/models/attention/backend.rs:1455-1498): causal
 // mask, optional window, scale as a parameter, softmax in float.  Value rows at or beyond what the tile may see are
@@ -38,14 +40,16 @@ constexpr int BKV = 128;                 // keys per block
 constexpr int HALF = BKV * 128;          // bytes of a [128 rows x 64 columns] half tile
 constexpr int TILE = 2 * HALF;           // bytes of a [128 x 128] bfloat16 tile
 constexpr int K_STAGES = 3, V_STAGES = 2;
-constexpr int THREADS = 192;             // warp 0: copies, warp 1: MMA, warps 2-5: softmax
+constexpr int THREADS = 320;             // warp 0: copies, warp 1: MMA, warps 2-9: softmax (two threads per query row)
 constexpr int TMEM_COLS = 512;           // S buffers (and P in their first 64 columns): columns 0..127 and 128..255; O: 256..383
 constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only growth beyond 2^8
 
-// Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers.
+// Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers and the softmax threads' exchange.
 constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, BAR_OFF = Q_OFF + TILE;
+constexpr int N_BARS = 2 * K_STAGES + 2 * V_STAGES + 2 + 3 + 4;
+constexpr int XCH_OFF = BAR_OFF + (N_BARS + 1) * 8;      // (one more slot holds the tensor-memory address)
+constexpr int SMEM_BYTES = XCH_OFF + 2 * 2 * 128 * 4;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
 }
@@ -54,28 +58,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = global_ns();
-  while (!mbar_try_wait(bar, parity)) {
-    if (global_ns() - start > 1000000000ull) {
-      atomicOr(err, B200_ERR_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-  return true;
 }
 // All lanes of a warp wait and agree on the outcome: the collective tensor-memory loads that follow need the
 // warp whole, also when a wait has run out.
@@ -197,7 +179,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   uint64_t* q_full = s_full + 2;
   uint64_t* p_full = q_full + 1;
   uint64_t* pv_done = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  uint64_t* pair_bar = pv_done + 1;                                  // [4]: the two softmax warps of each quarter
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -205,9 +188,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
     mbar_init(s_full, 1);
     mbar_init(s_full + 1, 1);
-    mbar_init(q_full, 4);
-    mbar_init(p_full, 4);
+    mbar_init(q_full, 8);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
+    for (int w = 0; w < 4; ++w) mbar_init(pair_bar + w, 2);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -314,17 +298,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       }
     }
   } else {
-    // ---- softmax warps: thread t owns query row t of the tile (tensor-memory lane t)
-    const int quarter = warp & 3;
+    // ---- softmax warps: two threads per query row.  Warps 2-5 take the first 64 keys of every block, warps 6-9
+    // the last 64; warp w reaches the tensor-memory lanes 32 (w mod 4) .. + 31, so the warps w and w + 4 share
+    // their rows.  The two threads of a row exchange their maxima (and at the end their sums) through shared
+    // memory and a barrier of their own.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int tok = r / group, head = head0 + r % group;
     const bool used = tok < ntok;
     const int qpos = used ? p_lo + tok : -1;
+    float* xch = reinterpret_cast<float*>(sm + XCH_OFF);          // [2 parities][2 halves][128 rows]
+    uint64_t* pair = pair_bar + quarter;
     if (nblk > 0) {
-      // Q row into its swizzled K-major tile (zeros for an unused row)
+      // Q row into its swizzled K-major tile (zeros for an unused row), eight chunks by each of the two threads
       const bf16* src = q + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = half * 8; c < half * 8 + 8; ++c) {
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (used) v = *reinterpret_cast<const uint4*>(src + c * 8);
         *reinterpret_cast<uint4*>(sm + Q_OFF + swz(r, c)) = v;
@@ -333,37 +322,43 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
     }
-    float m_ref = -INFINITY, l_run = 0.0f;             // reference maximum (log2 units) and the row sum relative to it
+    float m_ref = -INFINITY, l_run = 0.0f;             // reference maximum (log2 units) and this thread's part of the row sum
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
     for (int i = 0; i < nblk; ++i) {
-      const int first_key = k_begin + i * BKV;
+      const int blk_first = k_begin + i * BKV;
+      const int first_key = blk_first + half * 64;     // of this thread's 64 keys
       const uint32_t s_base = lane_base + (i & 1) * 128;
       if (!mbar_wait_warp(s_full + (i & 1), (i >> 1) & 1, err)) { ok = false; break; }
       tc_fence_after();
-      const bool masked = first_key + BKV - 1 > p_lo || first_key + BKV > kv_end || (window > 0 && first_key <= p_lo + ntok - 1 - window);
-      // pass 1: the row's maximum over the block's visible keys (of the raw scores; the scale is positive)
+      const bool masked = blk_first + BKV - 1 > p_lo || blk_first + BKV > kv_end || (window > 0 && blk_first <= p_lo + ntok - 1 - window);
+      // this thread's 64 scores stay in registers from here to the probabilities
+      float v[64];
+      tmem_ld64(s_base + half * 64, v);
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[64];
-        tmem_ld64(s_base + c * 64, v);
-        if (masked) {
+      if (masked) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int key = first_key + c * 64 + e;
-            const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
-            mx = fmaxf(mx, vis ? v[e] : -INFINITY);
-          }
-        } else {
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
-#pragma unroll
-          for (int e = 0; e < 64; e += 4) {
-            m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
-          }
-          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+        for (int e = 0; e < 64; ++e) {
+          const int key = first_key + e;
+          const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+          v[e] = vis ? v[e] : -INFINITY;
+          mx = fmaxf(mx, v[e]);
         }
+      } else {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
+#pragma unroll
+        for (int e = 0; e < 64; e += 4) {
+          m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
+      // The row's maximum over both halves.  Past this barrier both threads have read their scores, so the
+      // probabilities may overwrite them.
+      xch[((i & 1) * 2 + half) * 128 + r] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair);
+      if (!mbar_wait_warp(pair, i & 1, err)) { ok = false; break; }
+      mx = fmaxf(mx, xch[((i & 1) * 2 + (half ^ 1)) * 128 + r]);
       mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
       // The reference follows the maximum when it grew by more than the step (or there was none yet).
       const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
@@ -371,59 +366,46 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
       const float base = m_new == -INFINITY ? 0.0f : m_new;
       // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
+      // (Both warps of a pair see the same rows and maxima, so they decide alike; each takes 64 of the columns.)
       if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
         if (!mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          tmem_ld32(lane_base + 256 + c * 32, v);
+        for (int c = 0; c < 2; ++c) {
+          float o[32];
+          tmem_ld32(lane_base + 256 + half * 64 + c * 32, o);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] *= corr;
-          tmem_st32(lane_base + 256 + c * 32, v);
+          for (int e = 0; e < 32; ++e) o[e] *= corr;
+          tmem_st32(lane_base + 256 + half * 64 + c * 32, o);
         }
       }
       l_run = l_run * corr;
       m_ref = m_new;
-      // pass 2: probabilities relative to the reference and their sum.  The bfloat16 probabilities of columns
-      // 64c .. 64c + 63 go back into tensor memory, two to a column, over the scores that were just read (columns
-      // 32c .. 32c + 31 of this score buffer): the A operand of P V.  The buffer's next scores are issued behind
-      // that product.
+      // Probabilities relative to the reference and their sum.  The bfloat16 probabilities of this thread's 64 keys
+      // go back into tensor memory, two to a column (columns 32 half .. + 31 of this score buffer): the A operand
+      // of P V.  The buffer's next scores are issued behind that product.  (A hidden score is -inf and gives 0.)
       const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
+#pragma unroll
+      for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[64];
-        tmem_ld64(s_base + c * 64, v);
-        if (masked) {
+      uint32_t pr[32];
 #pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int key = first_key + c * 64 + e;
-            const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
-            v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
-        }
-        uint32_t pr[32];
-#pragma unroll
-        for (int e = 0; e < 64; e += 2) {
-          sum4[(e >> 1) & 3] += v[e] + v[e + 1];
-          __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
-          pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
-        }
-        tmem_st32_raw(s_base + c * 32, pr);
+      for (int e = 0; e < 64; e += 2) {
+        sum4[(e >> 1) & 3] += v[e] + v[e + 1];
+        __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
+        pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
       }
+      tmem_st32_raw(s_base + half * 32, pr);
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // value rows beyond what the tile may see must not reach P V, whatever the page or the stage held
-      if (first_key + BKV > kv_end) {
+      if (blk_first + BKV > kv_end) {
         const int s = i % V_STAGES;
         if (!mbar_wait_warp(v_full + s, (i / V_STAGES) & 1, err)) { ok = false; break; }      // the copies have landed
-        if (first_key + r >= kv_end) {
+        if (blk_first + r >= kv_end) {
           const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
+          for (int c = half * 8; c < half * 8 + 8; ++c)
+            *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
         }
         proxy_fence();                                 // the zeroed rows are visible to the tensor cores
       }
@@ -432,21 +414,29 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
+    if (ok && nblk > 0) {
+      // the row sum over both halves
+      xch[((nblk & 1) * 2 + half) * 128 + r] = l_run;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair);
+      ok = mbar_wait_warp(pair, nblk & 1, err);
+      if (ok) l_run += xch[((nblk & 1) * 2 + (half ^ 1)) * 128 + r];
+    }
     if (ok && nblk > 0) ok = mbar_wait_warp(pv_done, (nblk - 1) & 1, err);
     if (ok && nblk > 0) {
       tc_fence_after();
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
+      bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D + half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(lane_base + 256 + c * 32, v);        // (every lane of the warp takes part in the load)
+      for (int c = 0; c < 2; ++c) {
+        float o[32];
+        tmem_ld32(lane_base + 256 + half * 64 + c * 32, o);      // (every lane of the warp takes part in the load)
         if (used) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             __align__(16) bf16 y[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(v[q4 * 8 + e] * inv);
+            for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[q4 * 8 + e] * inv);
             *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = *reinterpret_cast<const uint4*>(y);
           }
         }
@@ -478,7 +468,7 @@ B200_EXPORT int b200_prefill_attention_tcgen05(const void* q, const void* k_map,
   if (group > BQ || BQ % group != 0) return B200_BAD_SIZE;
   const int box_rows = page_size < 32 ? page_size : 32;
   const int tile_tokens = BQ / group;
-  const size_t smem = 1024 + BAR_OFF + 16 * sizeof(uint64_t);
+  const size_t smem = 1024 + SMEM_BYTES;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

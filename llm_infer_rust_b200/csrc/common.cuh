@@ -91,6 +91,40 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// One poll of an mbarrier's phase (the instruction itself may suspend the thread for a short, bounded while).
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Waits for a phase of the barrier, but never for ever: after about a second it gives up, flags the engine's
+// error word and returns false (the caller's results are then meaningless, not hung).  Reading the global timer
+// costs far more than a poll and would sit between the barrier's completion and the waiter's next instruction,
+// so the clock is looked at only on every 64th failed poll.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t start = 0;
+  for (uint32_t polls = 1;; ++polls) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((polls & 63u) == 0u) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      if (now - start > 1000000000ull) {
+        atomicOr(err, B200_ERR_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
 // Programmatic dependent launch.  A kernel launched with b200_launch (below) may be scheduled while the kernel
 // before it in the stream is still running: what does not depend on that kernel (barrier set-up, fetching
 // weights) then overlaps its tail.  EVERY block of such a kernel calls pdl_wait() before it touches anything
