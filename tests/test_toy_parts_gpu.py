@@ -1,10 +1,12 @@
 """Parts that the framework does not ship, defined here and plugged in through the
 registries alone: a mixer with per-request state of its own (a linear recurrence),
 an architecture that alternates it with attention, runs one layer twice and lets
-the second run read the first run's keys and values.  Nothing under
-``llm_infer_rust_b200/`` knows these parts; the test registers, builds, loads and
-steps them, cut in different ways, and compares with a plain whole-sequence
-implementation written here.
+the second run read the first run's keys and values; and a second architecture
+with a feed-forward that routes every token to two of its experts (in one layer
+only, beside a dense one) and a position encoding of its own (a partial rotation
+over scaled positions).  Nothing under ``llm_infer_rust_b200/`` knows these parts;
+the tests register, build, load and step them, cut in different ways, and compare
+with plain whole-sequence implementations written here.
 """
 import dataclasses
 import math
@@ -216,6 +218,206 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     # the same slots are used again here: the state must start from zeros
     mixed = feed([[(1, 50), (2, 2)], [(1, 1), (2, 30), (3, 3)], [(1, 1), (2, 1), (3, 59)]] +
                  [[(1, 1), (2, 1), (3, 1)]] * 2 + [[(1, 1), (2, 1)]] * 2 + [[(1, 1)]] * 24)
+    for name, got in (("whole", whole), ("mixed", mixed)):
+        for r in seqs:
+            scale = max(1.0, np.abs(want[r]).max())
+            err = np.abs(got[r] - want[r]).max()
+            assert err <= 1e-5 * scale, (name, r, err)
+
+
+# ----------------------------------------------------------------------------- routed experts, another position encoding
+def register_routed_toys():
+    from llm_infer_rust_b200 import (Architecture, LayerSpec, ModelSpec, PartSpec, RunEntry,
+                                     register_architecture)
+    from llm_infer_rust_b200.kernels import ops
+    from llm_infer_rust_b200.parts import ParamDecl, Part, register_part
+    from llm_infer_rust_b200.weights import SourceTensor, WeightBinding
+
+    class ScaledPartialRope(Part):
+        """Rotates the first `rotary_dim` dims of a head (half-split pairs) by (p / position_scale) * theta^(-2i / rotary_dim).
+        It offers what the attention mixer asks of a position encoding: cos, sin [max_positions, rotary_dim / 2], rot_dim."""
+        category = "position_encoding"
+
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.rot_dim = int(spec["rotary_dim"])
+            i = torch.arange(0, self.rot_dim, 2, dtype=torch.float64)
+            inv_freq = float(spec["theta"]) ** (-i / self.rot_dim)
+            pos = torch.arange(int(spec["max_positions"]), dtype=torch.float64) / float(spec["position_scale"])
+            angle = pos[:, None] * inv_freq[None, :]
+            self.cos = torch.cos(angle).float().to(env.device).contiguous()
+            self.sin = torch.sin(angle).float().to(env.device).contiguous()
+
+    register_part("position_encoding", "toy_scaled_partial_rope", ScaledPartialRope, replace=True)
+
+    class TopTwoExperts(Part):
+        """Router logits in float; every token goes to its `top_k` experts, weighted by the softmax over the
+        chosen logits; each expert is a SwiGLU of its own.  The experts' matrices are stacked in two parameters."""
+        category = "feed_forward"
+
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.h, self.inter = int(spec["hidden_size"]), int(spec["expert_size"])
+            self.n, self.k = int(spec["num_experts"]), int(spec["top_k"])
+
+        def param_decls(self):
+            return {"router": ParamDecl((self.n, self.h)), "gate_up": ParamDecl((self.n * 2 * self.inter, self.h)),
+                    "down": ParamDecl((self.n * self.h, self.inter))}
+
+        def forward(self, x):
+            logits = ops.linear(x, self.params["router"]).float()
+            top, idx = logits.topk(self.k, dim=-1)
+            weight = torch.softmax(top, dim=-1)
+            out = torch.zeros(x.shape[0], self.h, dtype=torch.float32, device=x.device)
+            for e in range(self.n):
+                rows, slot = (idx == e).nonzero(as_tuple=True)
+                if rows.numel() == 0:
+                    continue
+                gu = ops.linear(x[rows].contiguous(), self.params["gate_up"][e * 2 * self.inter: (e + 1) * 2 * self.inter])
+                y = ops.linear(ops.silu_mul(gu), self.params["down"][e * self.h: (e + 1) * self.h])
+                out.index_add_(0, rows, y.float() * weight[rows, slot][:, None])
+            return out.to(x.dtype)
+
+    register_part("feed_forward", "toy_top_two_experts", TopTwoExperts, replace=True)
+
+    def parse(raw):
+        return dict(raw)
+
+    def model_spec(c):
+        h, d = c["hidden_size"], c["head_dim"]
+        norm = PartSpec("rms_norm", {"width": h, "eps": c["rms_norm_eps"]})
+        attn = PartSpec("gqa_attention", {"hidden_size": h, "num_heads": c["num_attention_heads"],
+                                          "num_kv_heads": c["num_key_value_heads"], "head_dim": d,
+                                          "qk_norm_eps": None, "window": None, "softmax_scale": c["softmax_scale"],
+                                          "position_encoding": "scaled"})
+        dense = PartSpec("swiglu", {"hidden_size": h, "intermediate_size": c["intermediate_size"]})
+        routed = PartSpec("toy_top_two_experts", {"hidden_size": h, "expert_size": c["expert_size"],
+                                                  "num_experts": c["num_experts"], "top_k": c["top_k"]})
+        block = PartSpec("pre_norm_deferred_add")
+        return ModelSpec(
+            architecture="ToyRoutedForCausalLM", vocab_size=c["vocab_size"], hidden_size=h,
+            max_positions=c["max_position_embeddings"],
+            embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": h}),
+            layers=(LayerSpec(block, attn, dense, norm), LayerSpec(block, attn, routed, norm)),
+            run_list=(RunEntry(0), RunEntry(1)), final_norm=norm,
+            lm_head=PartSpec("linear_head", {"vocab_size": c["vocab_size"], "hidden_size": h, "tied": False}),
+            position_encodings={"scaled": PartSpec("toy_scaled_partial_rope", {
+                "rotary_dim": c["rotary_dim"], "theta": c["rope_theta"], "position_scale": c["position_scale"],
+                "max_positions": c["max_position_embeddings"]})})
+
+    def weight_plan(c):
+        h, d, nh, nkv = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"]
+        plan = [WeightBinding("embedding.weight", (SourceTensor("embed", (c["vocab_size"], h)),)),
+                WeightBinding("final_norm.weight", (SourceTensor("norm", (h,), "norm"),)),
+                WeightBinding("lm_head.weight", (SourceTensor("head", (c["vocab_size"], h)),))]
+        for i in range(2):
+            plan += [WeightBinding(f"layers.{i}.input_norm.weight", (SourceTensor(f"l{i}.norm_in", (h,), "norm"),)),
+                     WeightBinding(f"layers.{i}.post_mixer_norm.weight", (SourceTensor(f"l{i}.norm_post", (h,), "norm"),)),
+                     WeightBinding(f"layers.{i}.mixer.qkv_proj", (SourceTensor(f"l{i}.q", (nh * d, h)),
+                                                                    SourceTensor(f"l{i}.k", (nkv * d, h)),
+                                                                    SourceTensor(f"l{i}.v", (nkv * d, h)))),
+                     WeightBinding(f"layers.{i}.mixer.o_proj", (SourceTensor(f"l{i}.o", (h, nh * d)),))]
+        inter, ex = c["intermediate_size"], c["expert_size"]
+        plan += [WeightBinding("layers.0.feed_forward.gate_up_proj", (SourceTensor("l0.gate", (inter, h)),
+                                                                      SourceTensor("l0.up", (inter, h)))),
+                 WeightBinding("layers.0.feed_forward.down_proj", (SourceTensor("l0.down", (h, inter)),)),
+                 WeightBinding("layers.1.feed_forward.router", (SourceTensor("l1.router", (c["num_experts"], h), "norm"),)),
+                 WeightBinding("layers.1.feed_forward.gate_up", tuple(
+                     SourceTensor(f"l1.e{e}.{n}", (ex, h)) for e in range(c["num_experts"]) for n in ("gate", "up"))),
+                 WeightBinding("layers.1.feed_forward.down", tuple(
+                     SourceTensor(f"l1.e{e}.down", (h, ex)) for e in range(c["num_experts"])))]
+        return plan
+
+    register_architecture(Architecture("ToyRoutedForCausalLM", "toy_routed", parse, model_spec, weight_plan),
+                          replace=True)
+
+
+ROUTED = {"model_type": "toy_routed", "architectures": ["ToyRoutedForCausalLM"], "hidden_size": 88,
+          "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 48, "rotary_dim": 32, "position_scale": 4.0,
+          "softmax_scale": 0.2, "intermediate_size": 120, "expert_size": 56, "num_experts": 5, "top_k": 2,
+          "vocab_size": 157, "rms_norm_eps": 1e-5, "rope_theta": 500.0, "max_position_embeddings": 128}
+
+
+def plain_routed_forward(w, ids):
+    c = ROUTED
+    w = {n: t.double() for n, t in w.items()}
+    T, d, rot = len(ids), c["head_dim"], c["rotary_dim"]
+    inv_freq = c["rope_theta"] ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot)
+    angle = (torch.arange(T, dtype=torch.float64) / c["position_scale"])[:, None] * inv_freq[None]
+    cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+
+    def rotate(x):                                             # [T, heads, d]: pairs (i, i + rot / 2) of the first rot dims
+        a, b, rest = x[..., : rot // 2], x[..., rot // 2: rot], x[..., rot:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], dim=-1)
+
+    h = P.plain_embedding(torch.tensor(ids), w["embed"])
+    residual = None
+    for i in range(2):
+        pre = f"l{i}."
+        if residual is None:
+            residual, x = h, P.plain_rms_norm(h, w[pre + "norm_in"], c["rms_norm_eps"])
+        else:
+            x, residual = P.plain_add_rms_norm(h, residual, w[pre + "norm_in"], c["rms_norm_eps"])
+        q, k, v = P.plain_qkv(x, w[pre + "q"], w[pre + "k"], w[pre + "v"], c["num_attention_heads"],
+                              c["num_key_value_heads"], d)
+        # (plain_attention divides by sqrt(d); this model's scale is a constant of its own)
+        a = P.plain_attention(rotate(q) * (c["softmax_scale"] * math.sqrt(d)), rotate(k), v) @ w[pre + "o"].T
+        x, residual = P.plain_add_rms_norm(a, residual, w[pre + "norm_post"], c["rms_norm_eps"])
+        if i == 0:
+            h = P.plain_swiglu(x, w["l0.gate"], w["l0.up"], w["l0.down"])
+        else:
+            logits = x @ w["l1.router"].T
+            top, idx = logits.topk(c["top_k"], dim=-1)
+            weight = torch.softmax(top, dim=-1)
+            h = torch.zeros_like(x)
+            for t in range(T):
+                for j in range(c["top_k"]):
+                    e = int(idx[t, j])
+                    y = P.plain_swiglu(x[t: t + 1], w[f"l1.e{e}.gate"], w[f"l1.e{e}.up"], w[f"l1.e{e}.down"])
+                    h[t] += weight[t, j] * y[0]
+    x, _ = P.plain_add_rms_norm(h, residual, w["norm"], c["rms_norm_eps"])
+    return P.plain_lm_head(x, w["head"])
+
+
+def test_a_routed_feed_forward_and_another_position_encoding(tmp_path):
+    register_routed_toys()
+    from llm_infer_rust_b200 import random_tensors, write_random_model
+    from llm_infer_rust_b200.engine import Engine, StepEntry
+    d = write_random_model(str(tmp_path), ROUTED, seed=6, std=0.05, norm_std=0.3)
+    w = random_tensors(ROUTED, 6, std=0.05, norm_std=0.3)
+    eng = Engine(d, dtype="float32", max_running_req=3, page_size=4, max_total_tokens=192, cuda_graph_bs=0)
+    assert type(eng.model.blocks[1].feed_forward).__name__ == "TopTwoExperts"
+    assert type(eng.model.blocks[0].feed_forward).__name__ != "TopTwoExperts"
+    g = torch.Generator().manual_seed(2)
+    seqs = {r: torch.randint(0, ROUTED["vocab_size"], (n,), generator=g).tolist() for r, n in ((1, 90), (2, 41))}
+    want = {r: plain_routed_forward(w, ids).numpy() for r, ids in seqs.items()}
+    # every expert is used by some token, and no expert by all
+    x = torch.randn(64, ROUTED["hidden_size"], generator=g)
+    chosen = (x.double() @ w["l1.router"].double().T).topk(2, dim=-1).indices
+    assert set(chosen.flatten().tolist()) == set(range(ROUTED["num_experts"]))
+
+    def feed(plan):
+        fed = {r: 0 for r in seqs}
+        got = {r: [] for r in seqs}
+        for step in plan:
+            entries = []
+            for r, n in step:
+                if fed[r] == 0:
+                    eng.open_request(r)
+                entries.append(StepEntry(r, seqs[r][fed[r]: fed[r] + n], list(range(n))))
+                fed[r] += n
+            logits = eng.step(entries).cpu().numpy()
+            at = 0
+            for r, n in step:
+                got[r].append(logits[at: at + n])
+                at += n
+        eng.check_kernel_errors()
+        for r in seqs:
+            eng.close_request(r)
+        return {r: np.concatenate(v) for r, v in got.items()}
+
+    whole = feed([[(1, 90)], [(2, 41)]])
+    mixed = feed([[(1, 60), (2, 2)], [(1, 1), (2, 30)], [(1, 2), (2, 1)]] + [[(1, 1), (2, 1)]] * 8 + [[(1, 1)]] * 19)
     for name, got in (("whole", whole), ("mixed", mixed)):
         for r in seqs:
             scale = max(1.0, np.abs(want[r]).max())
