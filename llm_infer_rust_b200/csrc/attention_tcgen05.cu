@@ -452,36 +452,348 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA.  What the kernel above reads per block of keys (K and V, 64 KB from L2) limits it on long
+// prompts: the tensor pipe and the softmax wait for the copies.  Here a CTA serves 256 query vectors, two tiles
+// A and B of consecutive tokens, and every K and V block is fetched once for both.  Tensor memory holds one score
+// buffer and one output accumulator per tile (4 x 128 columns); the MMA thread alternates between the tiles
+// (P V of tile A, the next S of tile A, P V of tile B, the next S of tile B), so one tile's products run under the
+// other tile's softmax.  Warps 2-5 are tile A's softmax (one thread per query row), warps 6-9 tile B's.
+constexpr int PAIR_K_STAGES = 3, PAIR_V_STAGES = 2;
+constexpr int PAIR_V_OFF = 0, PAIR_K_OFF = PAIR_V_STAGES * TILE, PAIR_Q_OFF = PAIR_K_OFF + PAIR_K_STAGES * TILE;
+constexpr int PAIR_BAR_OFF = PAIR_Q_OFF + 2 * TILE;
+constexpr int PAIR_N_BARS = 2 * PAIR_K_STAGES + 2 * PAIR_V_STAGES + 2 + 2 + 2 + 1;
+constexpr int PAIR_SMEM_BYTES = PAIR_BAR_OFF + (PAIR_N_BARS + 1) * 8;
+
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                            const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
+                            int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                            const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv,
+                            int page_size, int box_rows, int window, float scale_log2, int* err) {
+  constexpr int KS = PAIR_K_STAGES, VS = PAIR_V_STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(sm + PAIR_BAR_OFF);
+  uint64_t* k_empty = k_full + KS;
+  uint64_t* v_full = k_empty + KS;
+  uint64_t* v_empty = v_full + VS;
+  uint64_t* s_full = v_empty + VS;                                   // [2]: one per tile
+  uint64_t* p_full = s_full + 2;                                     // [2]
+  uint64_t* pv_done = p_full + 2;                                    // [2]
+  uint64_t* q_full = pv_done + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < KS; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+    for (int s = 0; s < VS; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(s_full + t, 1); mbar_init(p_full + t, 4); mbar_init(pv_done + t, 1); }
+    mbar_init(q_full, 8);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;        // columns: S of tile A 0..127, S of tile B 128..255, O of A 256..383, O of B 384..511
+  pdl_launch_dependents();
+  pdl_wait();
+
+  // Grid as above, with pairs of tiles in z.
+  const int row = rows[blockIdx.y];
+  const int kvh = blockIdx.x;
+  const int group = nh / nkv, head0 = kvh * group;
+  const int tile_tokens = BQ / group, pair_tokens = 2 * tile_tokens;
+  const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
+  const int pair = (q_len + pair_tokens - 1) / pair_tokens - 1 - static_cast<int>(blockIdx.z);
+  const bool active = pair >= 0;               // (an idle CTA still walks to the end, where tensor memory is freed)
+  const int prefix = prefix_len[row];
+  int tok0[2], ntok[2], p_lo[2], kv_end[2], nblk[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    tok0[t] = active ? pair * pair_tokens + t * tile_tokens : 0;
+    ntok[t] = active ? max(0, min(tile_tokens, q_len - tok0[t])) : 0;
+    p_lo[t] = prefix + tok0[t];
+    kv_end[t] = ntok[t] > 0 ? min(kv_len[row], p_lo[t] + ntok[t]) : 0;
+  }
+  // Both tiles walk the same blocks, from where tile A's window begins; tile B ends at or after tile A.
+  int k_begin = window > 0 ? max(0, p_lo[0] - window + 1) : 0;
+  k_begin -= k_begin % BKV;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) nblk[t] = ntok[t] > 0 ? (kv_end[t] - k_begin + BKV - 1) / BKV : 0;
+  const int nblk_all = max(nblk[0], nblk[1]);
+  const int kv_end_all = max(kv_end[0], kv_end[1]);
+  const int* table = block_table + static_cast<size_t>(row) * table_stride;
+
+  if (warp == 0) {
+    // ---- copies, as in the kernel above
+    bool ok = true;
+    auto fetch = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int first_key) {
+      const int n_sub = (min(BKV, kv_end_all - first_key) + box_rows - 1) / box_rows;
+      proxy_fence();
+      if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * box_rows * 128u);
+      __syncwarp();
+      for (int j = lane; j < n_sub; j += 32) {
+        const int key0 = first_key + j * box_rows;
+        const int page = table[key0 / page_size];
+        const int y = (page * nkv + kvh) * page_size + key0 % page_size;
+        tma_load_2d(dst + j * box_rows * 128, map, 0, y, bar);
+        tma_load_2d(dst + HALF + j * box_rows * 128, map, 64, y, bar);
+      }
+    };
+    int ik = 0;
+    for (int i = 0; i < nblk_all && ok; ++i) {
+      for (; ik < nblk_all && ik <= i + KS - 1 && ok; ++ik) {
+        const int s = ik % KS, use = ik / KS;
+        if (use > 0) ok = mbar_wait_warp(k_empty + s, (use - 1) & 1, err);
+        if (ok) fetch(&kmap, sm + PAIR_K_OFF + s * TILE, k_full + s, k_begin + ik * BKV);
+      }
+      if (!ok) break;
+      const int s = i % VS, use = i / VS;
+      if (use > 0) ok = mbar_wait_warp(v_empty + s, (use - 1) & 1, err);
+      if (ok) fetch(&vmap, sm + PAIR_V_OFF + s * TILE, v_full + s, k_begin + i * BKV);
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue (one lane)
+    if (lane == 0 && nblk_all > 0) {
+      bool ok = mbar_wait(q_full, 0, err);
+      // S of tile t over key block b; the block's last user gives the stage back
+      auto issue_s = [&](int t, int b) {                         // (t is a constant at every call)
+        const int s = b % KS;
+        if (!mbar_wait(k_full + s, (b / KS) & 1, err)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sm + PAIR_Q_OFF + t * TILE), k_addr = smem_u32(sm + PAIR_K_OFF + s * TILE);
+#pragma unroll
+        for (int j = 0; j < D / 16; ++j) {
+          const uint32_t off = (j >> 2) * HALF + (j & 3) * 32;
+          umma(tmem_base + t * 128, desc_k_major(q_addr + off), desc_k_major(k_addr + off), kDescQK, j > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full + t);
+        if (t == 1 || b >= nblk[1]) umma_commit(k_empty + s);
+        return true;
+      };
+      if (ok && nblk[0] > 0) ok = issue_s(0, 0);
+      if (ok && nblk[1] > 0) ok = issue_s(1, 0);
+      for (int b = 0; b < nblk_all && ok; ++b) {
+        const int s = b % VS;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (!ok || b >= nblk[t]) continue;
+          ok = mbar_wait(p_full + t, b & 1, err);            // P of block b lies where S of block b lay
+          if (ok) ok = mbar_wait(v_full + s, (b / VS) & 1, err);
+          if (!ok) continue;
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sm + PAIR_V_OFF + s * TILE);
+#pragma unroll
+          for (int j = 0; j < BKV / 16; ++j)
+            umma_a_tmem(tmem_base + 256 + t * 128, tmem_base + t * 128 + j * 8, desc_mn_major(v_addr + j * 16 * 128), kDescPV,
+                        (b > 0 || j > 0) ? 1u : 0u);
+          umma_commit(pv_done + t);
+          if (t == 1 || b >= nblk[1]) umma_commit(v_empty + s);
+          if (b + 1 < nblk[t]) ok = issue_s(t, b + 1);
+        }
+      }
+    }
+  } else {
+    // ---- softmax warps: thread (tile t, row r) owns one query row (tensor-memory lane r of the tile's columns)
+    const int t = (warp - 2) >> 2, quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int tok = r / group, head = head0 + r % group;
+    const int my_tok0 = t ? tok0[1] : tok0[0], my_ntok = t ? ntok[1] : ntok[0], my_p_lo = t ? p_lo[1] : p_lo[0];
+    const int my_kv_end = t ? kv_end[1] : kv_end[0], my_blocks = t ? nblk[1] : nblk[0];
+    const bool used = tok < my_ntok;
+    const int qpos = used ? my_p_lo + tok : -1;
+    if (nblk_all > 0) {
+      // Q row into its tile (zeros for an unused row, and for all rows of a tile without tokens)
+      const bf16* src = q + (static_cast<size_t>(q_begin + my_tok0 + tok) * nh + head) * D;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (used) v = *reinterpret_cast<const uint4*>(src + c * 8);
+        *reinterpret_cast<uint4*>(sm + PAIR_Q_OFF + t * TILE + swz(r, c)) = v;
+      }
+      proxy_fence();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_full);
+    }
+    float m_ref = -INFINITY, l_run = 0.0f;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_base = lane_base + t * 128, o_base = lane_base + 256 + t * 128;
+    bool ok = true;
+    for (int b = 0; b < my_blocks; ++b) {
+      const int first_key = k_begin + b * BKV;
+      if (!mbar_wait_warp(s_full + t, b & 1, err)) { ok = false; break; }
+      tc_fence_after();
+      const bool masked = first_key + BKV - 1 > my_p_lo || first_key + BKV > my_kv_end ||
+                          (window > 0 && first_key <= my_p_lo + my_ntok - 1 - window);
+      // pass 1: the row's maximum over the block's visible keys (of the raw scores; the scale is positive)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        float v[64];
+        tmem_ld64(s_base + c * 64, v);
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int key = first_key + c * 64 + e;
+            const bool vis = key <= qpos && key < my_kv_end && (window <= 0 || key > qpos - window);
+            mx = fmaxf(mx, vis ? v[e] : -INFINITY);
+          }
+        } else {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int e = 0; e < 64; e += 4) {
+            m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
+          }
+          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+        }
+      }
+      mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
+      const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
+      const float m_new = raise ? mx : m_ref;
+      const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
+      const float base = m_new == -INFINITY ? 0.0f : m_new;
+      // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
+      if (b > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
+        if (!mbar_wait_warp(pv_done + t, (b - 1) & 1, err)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          tmem_ld32(o_base + c * 32, o);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] *= corr;
+          tmem_st32(o_base + c * 32, o);
+        }
+      }
+      l_run = l_run * corr;
+      m_ref = m_new;
+      // pass 2: probabilities relative to the reference and their sum; the bfloat16 probabilities of columns
+      // 64c .. 64c + 63 go back into tensor memory over the scores just read (columns 32c .. 32c + 31).
+      const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        float v[64];
+        tmem_ld64(s_base + c * 64, v);
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int key = first_key + c * 64 + e;
+            const bool vis = key <= qpos && key < my_kv_end && (window <= 0 || key > qpos - window);
+            v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
+        }
+        uint32_t pr[32];
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          sum4[(e >> 1) & 3] += v[e] + v[e + 1];
+          __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
+          pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
+        }
+        tmem_st32_raw(s_base + c * 32, pr);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // Value rows beyond what the CTA may see must not reach P V, whatever the page or the stage held.  Both tiles
+      // write the same zeros, each before its own product.
+      if (first_key + BKV > kv_end_all) {
+        const int s = b % VS;
+        if (!mbar_wait_warp(v_full + s, (b / VS) & 1, err)) { ok = false; break; }
+        if (first_key + r >= kv_end_all) {
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            *reinterpret_cast<uint4*>(sm + PAIR_V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
+        }
+        proxy_fence();
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + t);
+    }
+    if (ok && my_blocks > 0) ok = mbar_wait_warp(pv_done + t, (my_blocks - 1) & 1, err);
+    if (ok && my_blocks > 0) {
+      tc_fence_after();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      bf16* dst = out + (static_cast<size_t>(q_begin + my_tok0 + tok) * nh + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float o[32];
+        tmem_ld32(o_base + c * 32, o);
+        if (used) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            __align__(16) bf16 y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[q4 * 8 + e] * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = *reinterpret_cast<const uint4*>(y);
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 B200_EXPORT int b200_attention_tcgen05_head_dim() { return D; }
 
 // Portions of prompts over a bfloat16 cache, head size 128; the number of query heads per KV head must divide 128
 // and the page size must be a power of two.  `k_map`, `v_map`: descriptors of b200_kv_tensor_map (attention_mma.cu)
 // with box_rows = min(page_size, 32).  Other arguments as b200_prefill_attention of attention.cu.
+// `variant`: 1 = one tile of 128 query vectors per CTA, 2 = two tiles per CTA, 0 = two tiles when the longest
+// row then still gives every SM a CTA (pairs halve the traffic per query but also the number of CTAs).
 B200_EXPORT int b200_prefill_attention_tcgen05(const void* q, const void* k_map, const void* v_map, void* out,
                                                const int* block_table, int table_stride, const int* cu_q,
                                                const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                                int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                               int* err, cudaStream_t stream) {
+                                               int variant, int* err, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || (page_size & (page_size - 1)) != 0) return B200_BAD_SIZE;
+  if (variant < 0 || variant > 2) return B200_BAD_SIZE;
   const int group = nh / nkv;
   if (group > BQ || BQ % group != 0) return B200_BAD_SIZE;
   const int box_rows = page_size < 32 ? page_size : 32;
   const int tile_tokens = BQ / group;
-  const size_t smem = 1024 + SMEM_BYTES;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0, n = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    sm_count = n;
+  }
+  const int n_pairs = (max_q_len + 2 * tile_tokens - 1) / (2 * tile_tokens);
+  const bool pairs = variant == 2 || (variant == 0 && static_cast<long long>(n_pairs) * nkv * n_rows >= sm_count);
+  const size_t smem = 1024 + (pairs ? PAIR_SMEM_BYTES : SMEM_BYTES);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(prefill_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + PAIR_SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   CUtensorMap kmap, vmap;
   memcpy(&kmap, k_map, sizeof(kmap));
   memcpy(&vmap, v_map, sizeof(vmap));
-  const int n_tiles = (max_q_len + tile_tokens - 1) / tile_tokens;
+  const int n_tiles = pairs ? n_pairs : (max_q_len + tile_tokens - 1) / tile_tokens;
   if (n_rows > 65535 || n_tiles > 65535) return B200_BAD_SIZE;      // the grid's y and z extents
   dim3 grid(nkv, n_rows, n_tiles);
-  return b200_launch(prefill_tcgen05_kernel, grid, dim3(THREADS), smem, stream, 0, kmap, vmap, static_cast<const bf16*>(q),
-                     static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size,
-                     box_rows, window, scale * 1.4426950408889634f, err);
+  return b200_launch(pairs ? prefill_tcgen05_pair_kernel : prefill_tcgen05_kernel, grid, dim3(THREADS), smem, stream, 0, kmap,
+                     vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
+                     prefix_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
 }

@@ -221,8 +221,12 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Ten
 
 # --------------------------------------------------------------------------- attention
 def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, n_rows,
-                      max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale) -> None:
-    """Causal attention of prompt portions over the paged cache (rows: which batch rows)."""
+                      max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale,
+                      tiles_per_cta: int = 0) -> None:
+    """Causal attention of prompt portions over the paged cache (rows: which batch rows).
+
+    ``tiles_per_cta`` (head size 128 on the tcgen05 kernel only): 1 or 2 tiles of 128 query vectors per
+    CTA, 0 lets the kernel's launcher choose by the size of the grid."""
     _cuda(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows)
     _contig(q, k_cache, v_cache, out, block_table)
     if n_rows == 0:
@@ -239,7 +243,8 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
             rc = load_cuda_library("attention_tcgen05.cu").b200_prefill_attention_tcgen05(
                 _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(block_table),
                 block_table.shape[-1], _p(cu_q), _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads,
-                num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), _p(error_word(q.device)), _stream())
+                num_kv_heads, page_size, int(window or 0), ctypes.c_float(scale), int(tiles_per_cta),
+                _p(error_word(q.device)), _stream())
             _ok(rc, "prefill_attention_tcgen05")
             return
         rc = _attention_mma(head_dim).b200_prefill_attention_mma(

@@ -405,11 +405,13 @@ def test_decode_attention(dtype, nh, nkv, d, page, window, splits):
     assert (out[6:] == 9.0).all()
 
 
+@pytest.mark.parametrize("tiles_per_cta", [1, 2, 0])
 @pytest.mark.parametrize("nh,nkv,window", [(16, 8, None), (8, 1, None), (4, 4, 200), (32, 8, 77)])
-def test_prefill_attention_over_many_key_blocks(nh, nkv, window):
+def test_prefill_attention_over_many_key_blocks(nh, nkv, window, tiles_per_cta):
     """Head size 128, rows that span up to nine blocks of 128 keys, prefixes that are no multiple of a block, and
     one stretch of keys four times as large as the rest: the running maximum jumps there (the output accumulated
-    so far is rescaled) and falls back behind it (the probabilities stay relative to the old maximum)."""
+    so far is rescaled) and falls back behind it (the probabilities stay relative to the old maximum).  With one
+    and with two tiles of 128 query vectors per CTA (rows whose second tile is short or empty among them)."""
     o = ops()
     d, page = 128, 16
     rows = [(0, 700), (300, 333), (1000, 130), (5, 1), (0, 128)]
@@ -421,7 +423,7 @@ def test_prefill_attention_over_many_key_blocks(nh, nkv, window):
     out = torch.full_like(c["q"], 9.0)
     serve = torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32, device=DEV)
     o.prefill_attention(c["q"], c["kc"], c["vc"], out, c["table"], c["cu"], c["kv_len"], c["prefix"], serve, 5,
-                        700, nh, nkv, d, page, window, scale)
+                        700, nh, nkv, d, page, window, scale, tiles_per_cta=tiles_per_cta)
     o.check_errors(torch.device(DEV))
     want = R.ref_paged_attention(c["q"], c["kc"], c["vc"], c["table"], c["cu"], c["kv_len"], c["prefix"], nh, nkv,
                                  d, page, window, scale)
