@@ -46,7 +46,7 @@ constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only g
 
 // Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers and the softmax threads' exchange.
 constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, BAR_OFF = Q_OFF + TILE;
-constexpr int N_BARS = 2 * K_STAGES + 2 * V_STAGES + 2 + 3 + 4;
+constexpr int N_BARS = 2 * K_STAGES + 2 * V_STAGES + 2 + 4 + 4;
 constexpr int XCH_OFF = BAR_OFF + (N_BARS + 1) * 8;      // (one more slot holds the tensor-memory address)
 constexpr int SMEM_BYTES = XCH_OFF + 2 * 2 * 128 * 4;
 
@@ -177,8 +177,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   uint64_t* v_empty = v_full + V_STAGES;                             // [2]
   uint64_t* s_full = v_empty + V_STAGES;                             // [2]
   uint64_t* q_full = s_full + 2;
-  uint64_t* p_full = q_full + 1;
-  uint64_t* pv_done = p_full + 1;
+  uint64_t* p_full = q_full + 1;                                     // [2]: one per score buffer, so that a softmax that runs
+  uint64_t* pv_done = p_full + 2;                                    //      a block ahead can never lap the MMA thread's wait
   uint64_t* pair_bar = pv_done + 1;                                  // [4]: the two softmax warps of each quarter
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
 
@@ -190,6 +190,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     mbar_init(s_full + 1, 1);
     mbar_init(q_full, 8);
     mbar_init(p_full, 8);
+    mbar_init(p_full + 1, 8);
     mbar_init(pv_done, 1);
     for (int w = 0; w < 4; ++w) mbar_init(pair_bar + w, 2);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -283,7 +284,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       if (ok && nblk > 1) ok = issue_s(1);
       for (int i = 0; i < nblk && ok; ++i) {
         const int s = i % V_STAGES;
-        ok = mbar_wait(p_full, i & 1, err);            // P of block i lies where S of block i lay
+        ok = mbar_wait(p_full + (i & 1), (i >> 1) & 1, err);      // P of block i lies where S of block i lay
         if (ok) ok = mbar_wait(v_full + s, (i / V_STAGES) & 1, err);
         if (!ok) break;
         tc_fence_after();
@@ -412,7 +413,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       tmem_wait_st();                                  // P is in tensor memory
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full + (i & 1));
     }
     if (ok && nblk > 0) {
       // the row sum over both halves
@@ -459,7 +460,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
 // buffer and one output accumulator per tile (4 x 128 columns); the MMA thread alternates between the tiles
 // (P V of tile A, the next S of tile A, P V of tile B, the next S of tile B), so one tile's products run under the
 // other tile's softmax.  Warps 2-5 are tile A's softmax (one thread per query row), warps 6-9 tile B's.
-constexpr int PAIR_K_STAGES = 3, PAIR_V_STAGES = 2;
+// (Blocks of 64 keys, which leave room for two score buffers per tile, were tried and were slower: twice the
+// hand-overs per key.)  A tile's softmax of block b + 1 needs S of block b + 1, which is issued behind P V of block b:
+// no barrier of a tile can complete two phases while someone still waits for the first.
+constexpr int PAIR_K_STAGES = 2, PAIR_V_STAGES = 2;      // (deeper rings were slower: more copies in flight, same traffic)
 constexpr int PAIR_V_OFF = 0, PAIR_K_OFF = PAIR_V_STAGES * TILE, PAIR_Q_OFF = PAIR_K_OFF + PAIR_K_STAGES * TILE;
 constexpr int PAIR_BAR_OFF = PAIR_Q_OFF + 2 * TILE;
 constexpr int PAIR_N_BARS = 2 * PAIR_K_STAGES + 2 * PAIR_V_STAGES + 2 + 2 + 2 + 1;
@@ -561,17 +565,25 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
     // ---- MMA issue (one lane)
     if (lane == 0 && nblk_all > 0) {
       bool ok = mbar_wait(q_full, 0, err);
+      // The operand descriptors differ only in their start address (the low 14 bits, in units of 16 bytes, which never
+      // carry here): built once, then a stage or a tile is an addition.
+      uint64_t dq[D / 16], dk[D / 16], dv[BKV / 16];
+#pragma unroll
+      for (int j = 0; j < D / 16; ++j) {
+        const uint32_t off = (j >> 2) * HALF + (j & 3) * 32;
+        dq[j] = desc_k_major(smem_u32(sm + PAIR_Q_OFF) + off);
+        dk[j] = desc_k_major(smem_u32(sm + PAIR_K_OFF) + off);
+      }
+#pragma unroll
+      for (int j = 0; j < BKV / 16; ++j) dv[j] = desc_mn_major(smem_u32(sm + PAIR_V_OFF) + j * 16 * 128);
       // S of tile t over key block b; the block's last user gives the stage back
       auto issue_s = [&](int t, int b) {                         // (t is a constant at every call)
         const int s = b % KS;
         if (!mbar_wait(k_full + s, (b / KS) & 1, err)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sm + PAIR_Q_OFF + t * TILE), k_addr = smem_u32(sm + PAIR_K_OFF + s * TILE);
+        const uint64_t q_step = static_cast<uint64_t>(t * (TILE >> 4)), k_step = static_cast<uint64_t>(s * (TILE >> 4));
 #pragma unroll
-        for (int j = 0; j < D / 16; ++j) {
-          const uint32_t off = (j >> 2) * HALF + (j & 3) * 32;
-          umma(tmem_base + t * 128, desc_k_major(q_addr + off), desc_k_major(k_addr + off), kDescQK, j > 0 ? 1u : 0u);
-        }
+        for (int j = 0; j < D / 16; ++j) umma(tmem_base + t * 128, dq[j] + q_step, dk[j] + k_step, kDescQK, j > 0 ? 1u : 0u);
         umma_commit(s_full + t);
         if (t == 1 || b >= nblk[1]) umma_commit(k_empty + s);
         return true;
@@ -587,11 +599,10 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
           if (ok) ok = mbar_wait(v_full + s, (b / VS) & 1, err);
           if (!ok) continue;
           tc_fence_after();
-          const uint32_t v_addr = smem_u32(sm + PAIR_V_OFF + s * TILE);
+          const uint64_t v_step = static_cast<uint64_t>(s * (TILE >> 4));
 #pragma unroll
           for (int j = 0; j < BKV / 16; ++j)
-            umma_a_tmem(tmem_base + 256 + t * 128, tmem_base + t * 128 + j * 8, desc_mn_major(v_addr + j * 16 * 128), kDescPV,
-                        (b > 0 || j > 0) ? 1u : 0u);
+            umma_a_tmem(tmem_base + 256 + t * 128, tmem_base + t * 128 + j * 8, dv[j] + v_step, kDescPV, (b > 0 || j > 0) ? 1u : 0u);
           umma_commit(pv_done + t);
           if (t == 1 || b >= nblk[1]) umma_commit(v_empty + s);
           if (b + 1 < nblk[t]) ok = issue_s(t, b + 1);
