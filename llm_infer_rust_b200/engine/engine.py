@@ -443,8 +443,13 @@ class Engine:
                 if e.sample:
                     rows.append((self._params[e.uid], self._seeds[e.uid], e.output_index))
             logits = self.step(entries)
-            sampled = self.sampler.sample(logits, rows) if rows else []
-            self.check_kernel_errors()
+            if rows:
+                sampled = ops.read_ids_and_check(self.sampler.sample_device(logits, rows))
+                if any(i < 0 for i in sampled):
+                    raise RuntimeError("sampling produced no valid token for a row (were the logits finite?)")
+            else:
+                sampled = []
+                self.check_kernel_errors()
         except Exception:
             out += sched.fail_step(plan)
             self.last_step_error = True

@@ -38,7 +38,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC"
               "--expt-relaxed-constexpr"]
 
 _lock = threading.Lock()
-_loaded: Dict[str, object] = {}
+_loaded: Dict[str, object] = {}        # library path -> loaded library
+_by_name: Dict[tuple, object] = {}       # (source, defines) -> loaded library
 
 
 class BuildError(RuntimeError):
@@ -167,12 +168,21 @@ def build_cuda_library(source: str, defines: Optional[Dict[str, object]] = None)
 
 
 def load_cuda_library(source: str, defines: Optional[Dict[str, object]] = None) -> ctypes.CDLL:
+    """The loaded library of ``source`` compiled with ``defines``; compiled at the first call.
+
+    Every kernel call comes through here, so a process looks a library up by name; the
+    sources are hashed (and compiled, if that hash has no library yet) only the first time."""
+    name = (source, tuple(sorted(defines.items())) if defines else ())
+    lib = _by_name.get(name)
+    if lib is not None:
+        return lib
     key = cuda_library_path(source, defines)
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
             lib = ctypes.CDLL(build_cuda_library(source, defines))
             _loaded[key] = lib
+        _by_name[name] = lib
         return lib
 
 

@@ -98,6 +98,30 @@ def check_errors(device: torch.device) -> None:
         raise KernelError("a kernel refused an access: " + "; ".join(what))
 
 
+_staging = {}
+
+
+def read_ids_and_check(ids: torch.Tensor) -> list:
+    """Token ids (int32, on the device) as a host list, and the error word with them: two small copies into
+    pinned memory and ONE wait for the stream, instead of a blocking read each.  Raises as check_errors does."""
+    device = ids.device
+    key = device.index or 0
+    n = ids.numel()
+    buf = _staging.get(key)
+    if buf is None or buf.numel() < n + 1:
+        buf = _staging[key] = torch.empty(max(1024, 2 * (n + 1)), dtype=torch.int32).pin_memory()
+    word = error_word(device)
+    buf[:n].copy_(ids.reshape(-1), non_blocking=True)
+    buf[n:n + 1].copy_(word, non_blocking=True)
+    torch.cuda.current_stream(device).synchronize()
+    value = int(buf[n])
+    if value:
+        word.zero_()
+        what = [text for bit, text in ERROR_BITS.items() if value & bit]
+        raise KernelError("a kernel refused an access: " + "; ".join(what))
+    return buf[:n].tolist()
+
+
 # --------------------------------------------------------------------------- libraries
 def _elementwise():
     return load_cuda_library("elementwise.cu")
