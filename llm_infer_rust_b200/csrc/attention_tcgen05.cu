@@ -368,8 +368,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       const float base = m_new == -INFINITY ? 0.0f : m_new;
       // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
       // (Both warps of a pair see the same rows and maxima, so they decide alike; each takes 64 of the columns.)
+      bool pv_seen = i == 0;                             // whether this block has looked at P V of the block before
       if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
         if (!mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
+        pv_seen = true;
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
@@ -411,6 +413,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
         proxy_fence();                                 // the zeroed rows are visible to the tensor cores
       }
       tmem_wait_st();                                  // P is in tensor memory
+      // Every phase of pv_done is waited for, in order: a wait by parity cannot tell "phase i - 1 is not finished"
+      // from "phase i - 2 is not finished", and a waiter two phases ahead would pass at once.  Here, at the end of
+      // the block's work, P V of the block before has long finished.
+      if (!pv_seen && !mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + (i & 1));
@@ -669,8 +675,10 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
       const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
       const float base = m_new == -INFINITY ? 0.0f : m_new;
       // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
+      bool pv_seen = b == 0;                             // whether this block has looked at P V of the block before
       if (b > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
         if (!mbar_wait_warp(pv_done + t, (b - 1) & 1, err)) { ok = false; break; }
+        pv_seen = true;
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -726,6 +734,8 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
         proxy_fence();
       }
       tmem_wait_st();
+      // every phase of pv_done is waited for, in order (see the kernel above)
+      if (!pv_seen && !mbar_wait_warp(pv_done + t, (b - 1) & 1, err)) { ok = false; break; }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + t);

@@ -365,6 +365,7 @@ def paged_case(rows, nh, nkv, d, page, dtype, seed=0, poison=True):
 ATT_CASES = [  # nh, nkv, d, page, window
     (4, 2, 16, 4, None), (6, 2, 32, 16, None), (5, 5, 48, 8, 40), (8, 1, 128, 16, None),
     (16, 2, 64, 1, 7), (3, 1, 80, 64, None), (2, 2, 256, 16, 33), (32, 8, 128, 16, None),
+    (8, 2, 128, 4, None), (16, 4, 128, 64, 100),
 ]
 
 
@@ -406,14 +407,15 @@ def test_decode_attention(dtype, nh, nkv, d, page, window, splits):
 
 
 @pytest.mark.parametrize("tiles_per_cta", [1, 2, 0])
-@pytest.mark.parametrize("nh,nkv,window", [(16, 8, None), (8, 1, None), (4, 4, 200), (32, 8, 77)])
-def test_prefill_attention_over_many_key_blocks(nh, nkv, window, tiles_per_cta):
+@pytest.mark.parametrize("nh,nkv,window,page", [(16, 8, None, 16), (8, 1, None, 4), (4, 4, 200, 64), (32, 8, 77, 16),
+                                                (6, 2, None, 128)])
+def test_prefill_attention_over_many_key_blocks(nh, nkv, window, page, tiles_per_cta):
     """Head size 128, rows that span up to nine blocks of 128 keys, prefixes that are no multiple of a block, and
     one stretch of keys four times as large as the rest: the running maximum jumps there (the output accumulated
     so far is rescaled) and falls back behind it (the probabilities stay relative to the old maximum).  With one
     and with two tiles of 128 query vectors per CTA (rows whose second tile is short or empty among them)."""
     o = ops()
-    d, page = 128, 16
+    d = 128
     rows = [(0, 700), (300, 333), (1000, 130), (5, 1), (0, 128)]
     c = paged_case(rows, nh, nkv, d, page, torch.bfloat16, seed=7)
     for r, (p, n) in enumerate(rows):
