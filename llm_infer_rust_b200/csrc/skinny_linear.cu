@@ -107,6 +107,9 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   constexpr int BN = 64 * MT;
   constexpr int STAGE_BYTES = BN * 128;
   constexpr int STAGES = W_RING_BYTES / STAGE_BYTES;
+  // A stage's uses all fall to one group (k-block it -> stage it % STAGES, group it % GROUPS), so that group waits
+  // for every phase of the stage's barrier in order; a waiter by parity that skipped a phase could pass too early.
+  static_assert(STAGES % GROUPS == 0, "every stage of the ring must belong to one group of warps");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   bf16* xs = reinterpret_cast<bf16*>(ring + W_RING_BYTES);                     // [mpad][ldx]
