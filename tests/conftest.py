@@ -66,6 +66,12 @@ TINY = {
                         head_dim=64, intermediate_size=200, vocab_size=333, rope_theta=1e5,
                         rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=256),
               seed=3, norm_std=0.1, page_size=16),
+    # E has the head size (128) of the tcgen05 attention kernels: portions of 64 tokens or more go through them,
+    # shorter ones and decoded tokens through the mma.sync kernels and the fused QKV product.
+    "E": dict(raw=_base(num_hidden_layers=2, hidden_size=192, num_attention_heads=4, num_key_value_heads=2,
+                        head_dim=128, intermediate_size=328, vocab_size=307, rope_theta=1e6,
+                        rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=512),
+              seed=4, norm_std=0.1, page_size=16),
 }
 
 

@@ -15,7 +15,7 @@ import plain_qwen3 as P
 
 
 def test_causality(tiny, tiny_weights):
-    for name in ("A", "B", "C", "D"):
+    for name in ("A", "B", "C", "D", "E"):
         raw, w = tiny[name]["raw"], tiny_weights[name]
         g = torch.Generator().manual_seed(3)
         ids = torch.randint(0, raw["vocab_size"], (50,), generator=g).tolist()

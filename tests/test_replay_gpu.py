@@ -24,7 +24,7 @@ from replay_driver import Replay, mixed_schedule, run_alone
 pytestmark = pytest.mark.gpu
 
 TOL = {"float32": 1e-5, "bfloat16": 2.0 ** -5}
-LENGTHS = {"A": 120, "B": 250, "C": 300, "D": 250}
+LENGTHS = {"A": 120, "B": 250, "C": 300, "D": 250, "E": 380}
 
 
 def tokens(vocab, n, seed):
@@ -58,7 +58,7 @@ def model_dir(tiny_dirs, tiny, tiny_weights, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_alone_whole_decoded_and_in_portions(name, dtype, tiny, tiny_weights, tiny_dirs, tmp_path):
     raw, page = tiny[name]["raw"], tiny[name]["page_size"]
     vocab, T = raw["vocab_size"], LENGTHS[name]
@@ -93,7 +93,7 @@ def test_alone_whole_decoded_and_in_portions(name, dtype, tiny, tiny_weights, ti
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_with_pages_used_again(name, dtype, tiny, tiny_weights, tiny_dirs, tmp_path):
     raw, page = tiny[name]["raw"], tiny[name]["page_size"]
     vocab, longest = raw["vocab_size"], LENGTHS[name]
