@@ -1,0 +1,87 @@
+"""Layers of real size: the bfloat16 engine against the float32 engine on the same weights.
+
+The tiny configurations do not reach what only real sizes switch on: the tcgen05 attention kernels with a grid
+larger than the machine (two query tiles per CTA), cluster split-K in the few-row product, the tcgen05 product with
+the SwiGLU epilogue, the decode kernel with several splits, CUDA graphs over real layer sizes.  Here models with
+the layer sizes of Qwen3-0.6B and Qwen3-8B (fewer layers, a smaller vocabulary) run the same token sequences through
+the float32 engine (true 32-bit kernels, checked against the plain implementation on the tiny configurations) and
+through the bfloat16 engine; both read the same bfloat16-rounded weights.
+
+Tolerance as in the replay tests: 2^-5 of the logits' scale.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BASE = {"model_type": "qwen3", "architectures": ["Qwen3ForCausalLM"], "eos_token_id": None, "hidden_act": "silu",
+        "attention_bias": False, "head_dim": 128, "vocab_size": 4099, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
+        "max_position_embeddings": 4096}
+SHAPES = {
+    # the layer sizes of Qwen3-0.6B and of Qwen3-8B (where the tcgen05 product with the SwiGLU epilogue pays)
+    "0.6b": dict(BASE, num_hidden_layers=3, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True),
+    "8b": dict(BASE, num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+               intermediate_size=12288, tie_word_embeddings=False),
+}
+
+
+def tokens(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, BASE["vocab_size"], (n,), generator=g).tolist()
+
+
+def run(engine, plan, seqs):
+    """plan: steps of (request, count); every fed position's logits come back, per request in order."""
+    from llm_infer_rust_b200.engine import StepEntry
+    fed = {r: 0 for r in seqs}
+    got = {r: [] for r in seqs}
+    for step in plan:
+        entries = []
+        for r, n in step:
+            if fed[r] == 0:
+                engine.open_request(r)
+            # all positions of short portions, the last position of long ones (a logits row is 16 KB)
+            want = list(range(n)) if n <= 64 else [n - 1]
+            entries.append((r, n, want, StepEntry(r, seqs[r][fed[r]: fed[r] + n], want)))
+            fed[r] += n
+        logits = engine.step([e[3] for e in entries]).float().cpu().numpy()
+        at = 0
+        for r, n, want, _ in entries:
+            got[r].append(logits[at: at + len(want)])
+            at += len(want)
+    engine.check_kernel_errors()
+    for r in seqs:
+        engine.close_request(r)
+    return {r: np.concatenate(v) for r, v in got.items()}
+
+
+@pytest.mark.parametrize("shape", sorted(SHAPES))
+def test_bfloat16_engine_agrees_with_the_float32_engine_at_real_layer_sizes(shape, tmp_path):
+    from llm_infer_rust_b200 import write_random_model
+    from llm_infer_rust_b200.engine import Engine
+    # stored in bfloat16: the float32 engine widens the same values
+    folder = write_random_model(str(tmp_path), SHAPES[shape], seed=11, std=0.03 if shape == "0.6b" else 0.015,
+                                norm_std=0.1, dtype="bfloat16")
+    seqs = {1: tokens(2700, 1), 2: tokens(333, 2), 3: tokens(40, 3)}
+    # request 1: 2,560 tokens at once (160 pairs of tiles for 8 KV heads: the two-tile attention kernel), then a
+    # portion of 100 over that prefix, then single tokens; request 2: whole (one tile per CTA), request 3 beside
+    # decoded tokens of the others, in steps of at most 16 tokens (the few-row product, the decode kernel in splits)
+    plan = [[(1, 2560)], [(1, 100), (2, 333)], [(1, 1), (3, 14)], [(1, 1), (3, 1)]] + [[(1, 1), (3, 1)]] * 6 + \
+           [[(1, 1)]] * 8 + [[(3, 8)]]
+    common = dict(max_running_req=4, page_size=16, max_total_tokens=4096, max_seq_len=2800)
+    ref = run(Engine(folder, dtype="float32", cuda_graph_bs=0, **common), plan, seqs)
+    eng = Engine(folder, dtype="bfloat16", cuda_graph_bs=4, **common)
+    got = run(eng, plan, seqs)
+    again = run(eng, plan, seqs)                       # the decode graphs are captured by now: replayed here
+    for r in seqs:
+        scale = max(1.0, float(np.abs(ref[r]).max()))
+        for name, g in (("first run", got[r]), ("with graphs replayed", again[r])):
+            assert g.shape == ref[r].shape
+            err = np.abs(g - ref[r]).max(axis=1)
+            worst = int(err.argmax())
+            assert err[worst] <= 2.0 ** -5 * scale, \
+                f"request {r}, {name}: row {worst} is off by {err[worst]:.3e} (allowed {2.0 ** -5 * scale:.3e})"
+        # the same kernels ran both times
+        assert np.abs(got[r] - again[r]).max() <= 2.0 ** -7 * scale
