@@ -772,6 +772,10 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
 
 B200_EXPORT int b200_attention_tcgen05_head_dim() { return D; }
 
+// How many launches took the one-tile and the two-tile kernel so far (tests ask which path a model reached).
+static long long g_launches[2] = {0, 0};
+B200_EXPORT long long b200_attention_tcgen05_launches(int two_tiles) { return g_launches[two_tiles ? 1 : 0]; }
+
 // Portions of prompts over a bfloat16 cache, head size 128; the number of query heads per KV head must divide 128
 // and the page size must be a power of two.  `k_map`, `v_map`: descriptors of b200_kv_tensor_map (attention_mma.cu)
 // with box_rows = min(page_size, 32).  Other arguments as b200_prefill_attention of attention.cu.
@@ -814,6 +818,7 @@ B200_EXPORT int b200_prefill_attention_tcgen05(const void* q, const void* k_map,
   const int n_tiles = pairs ? n_pairs : (max_q_len + tile_tokens - 1) / tile_tokens;
   if (n_rows > 65535 || n_tiles > 65535) return B200_BAD_SIZE;      // the grid's y and z extents
   dim3 grid(nkv, n_rows, n_tiles);
+  ++g_launches[pairs ? 1 : 0];
   return b200_launch(pairs ? prefill_tcgen05_pair_kernel : prefill_tcgen05_kernel, grid, dim3(THREADS), smem, stream, 0, kmap,
                      vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
                      prefix_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);

@@ -244,6 +244,13 @@ def qkv_post(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Ten
 
 
 # --------------------------------------------------------------------------- attention
+def tcgen05_attention_launches() -> tuple:
+    """(launches of the one-tile kernel, launches of the two-tile kernel) of the tcgen05 prefill attention so far."""
+    lib = load_cuda_library("attention_tcgen05.cu")
+    lib.b200_attention_tcgen05_launches.restype = ctypes.c_longlong
+    return int(lib.b200_attention_tcgen05_launches(0)), int(lib.b200_attention_tcgen05_launches(1))
+
+
 def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefix_len, rows, n_rows,
                       max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, scale,
                       tiles_per_cta: int = 0) -> None:

@@ -73,7 +73,11 @@ def test_bfloat16_engine_agrees_with_the_float32_engine_at_real_layer_sizes(shap
     common = dict(max_running_req=4, page_size=16, max_total_tokens=4096, max_seq_len=2800)
     ref = run(Engine(folder, dtype="float32", cuda_graph_bs=0, **common), plan, seqs)
     eng = Engine(folder, dtype="bfloat16", cuda_graph_bs=4, **common)
+    from llm_infer_rust_b200.kernels import ops
+    one_before, two_before = ops.tcgen05_attention_launches()
     got = run(eng, plan, seqs)
+    one_after, two_after = ops.tcgen05_attention_launches()
+    assert two_after > two_before and one_after > one_before, "both tcgen05 attention kernels must have run"
     again = run(eng, plan, seqs)                       # the decode graphs are captured by now: replayed here
     for r in seqs:
         scale = max(1.0, float(np.abs(ref[r]).max()))
