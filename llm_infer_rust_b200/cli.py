@@ -24,6 +24,8 @@ Options (as in the reference where it has them):
   --cuda-graph-bs N         Maximum CUDA decode graph batch (0 disables; default max-running-req)
   --prefill-cuda-graph-max-tokens N  Largest step with prompt tokens that is captured as a CUDA graph when its
                             shape repeats (0 disables; default 2048)
+  --disable-cpu-gpu-overlap Read every step's tokens before the next step is put on the GPU (default: a step of
+                            decoded tokens is launched before the step before it has reported)
   --max-seq-len N           Maximum sequence length (default 8192, at most the model's; must not exceed model config)
   --page-size N             KV cache page size (default 16)
   --dtype NAME              Model dtype: auto, bfloat16, float32
@@ -51,6 +53,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--chunked-prefill-size", type=int, default=None)
     p.add_argument("--cuda-graph-bs", type=int, default=None)
     p.add_argument("--prefill-cuda-graph-max-tokens", type=int, default=2048)
+    p.add_argument("--disable-cpu-gpu-overlap", action="store_true")
     p.add_argument("--max-seq-len", type=int, default=None)
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--dtype", default="auto", choices=["auto", "bfloat16", "float32"])
@@ -113,7 +116,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                     max_prefill_tokens_per_batch=args.max_prefill_tokens_per_batch,
                     chunked_prefill_size=args.chunked_prefill_size, cuda_graph_bs=args.cuda_graph_bs,
                     prefill_cuda_graph_max_tokens=args.prefill_cuda_graph_max_tokens,
-                    seed=args.seed, log_level=args.log_level)
+                    cpu_gpu_overlap=not args.disable_cpu_gpu_overlap, seed=args.seed, log_level=args.log_level)
     params = SamplingParams(args.temperature, args.top_k, args.top_p, args.ignore_eos, args.max_tokens,
                             args.seed if args.seed else None)
     for prompt, result in zip(prompts, engine.generate(prompts, params)):

@@ -112,6 +112,7 @@ PYBIND11_MODULE(_host_runtime, m) {
       .def("abort_request", &Scheduler::abort_request)
       .def("is_idle", &Scheduler::is_idle)
       .def("plan_step", &Scheduler::plan_step)
+      .def("successor", &Scheduler::successor)
       .def("tokens_of", &Scheduler::tokens_of)
       .def("params_of", &Scheduler::params_of)
       .def("commit_step", &Scheduler::commit_step)

@@ -131,6 +131,22 @@ StepPlan Scheduler::plan_step() {
   return plan;
 }
 
+StepPlan Scheduler::successor(const StepPlan& plan) const {
+  StepPlan next;
+  if (!pending_.empty() || plan.entries.size() != running_.size()) return next;
+  for (const PlanEntry& e : plan.entries) {
+    const Request* r = nullptr;
+    for (const Request& q : running_)
+      if (q.uid == e.uid) { r = &q; break; }
+    // after `plan`: one more output, one more token in the sequence
+    if (!r || !e.sample || e.output_index + 1 >= r->params.max_tokens || e.start + e.count + 1 >= opt_.max_seq_len)
+      return StepPlan();
+    next.entries.push_back({e.uid, e.start + e.count, 1, true, e.output_index + 1});
+  }
+  next.decode_rows = static_cast<int>(next.entries.size());
+  return next;
+}
+
 std::vector<int> Scheduler::tokens_of(const PlanEntry& e) const {
   const Request* r = find_any(e.uid);
   if (!r) throw std::invalid_argument("plan entry of an unknown request");
@@ -144,7 +160,13 @@ std::vector<OutputToken> Scheduler::commit_step(const StepPlan& plan, const std:
   size_t next = 0;
   for (const PlanEntry& e : plan.entries) {
     Request* r = find_running(e.uid);
-    if (!r) continue;   // aborted while the step ran
+    if (!r) {           // finished or aborted while the step ran: its token is dropped
+      if (e.sample) {
+        if (next >= sampled.size()) throw std::invalid_argument("fewer sampled tokens than sampling rows");
+        ++next;
+      }
+      continue;
+    }
     r->cursor = e.start + e.count;
     if (!e.sample) continue;
     if (next >= sampled.size()) throw std::invalid_argument("fewer sampled tokens than sampling rows");

@@ -17,7 +17,12 @@
 //  * finish: Stop on an end-of-sequence id (unless ignore_eos), Length when
 //    max_tokens outputs exist or the sequence reaches max_seq_len
 //    (scheduler.rs:570-578); the finishing token is emitted; pages and the
-//    state slot are given back at once.
+//    state slot are given back at once;
+//  * a step that needs no decision can be planned before the step before it has reported its tokens
+//    (successor(); after the reference's overlap of host and device work, scheduler.rs:935-1038): when
+//    nothing waits, every running request sampled in the step and none of them can end by length, the
+//    next step is one decoded token for each of them.  A request that ends on a stop id (or is aborted)
+//    while its successor step already runs stays in that step as a dead row; commit_step drops its token.
 #pragma once
 #include <cstdint>
 #include <deque>
@@ -77,10 +82,14 @@ class Scheduler {
   bool is_idle() const { return pending_.empty() && running_.empty() && outbox_.empty(); }
 
   StepPlan plan_step();
+  // The step after `plan`, if it can be known before `plan` is committed (see above); else no entries.  Its
+  // entries stand in the order of `plan`'s, so the tokens sampled by `plan` are its inputs row by row.
+  StepPlan successor(const StepPlan& plan) const;
   // Tokens of a planned portion, to hand to the engine.
   std::vector<int> tokens_of(const PlanEntry& e) const;
   SamplingParams params_of(int64_t uid) const;
-  // `sampled` holds one token for each entry with sample == true, in order.
+  // `sampled` holds one token for each entry with sample == true, in order (also for entries whose request
+  // is gone by now: those tokens are dropped).
   std::vector<OutputToken> commit_step(const StepPlan& plan, const std::vector<int>& sampled);
   // The step failed: every request in it finishes with Error and frees its pages.
   std::vector<OutputToken> fail_step(const StepPlan& plan);

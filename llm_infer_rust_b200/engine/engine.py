@@ -121,13 +121,21 @@ class _DecodeGraph:
         self.launches = 0          # kernels of this package inside the graph
 
 
+@dataclass
+class _Flight:
+    """A step that is on the GPU: its plan, its sampled ids on the device, their read-back."""
+    plan: object
+    ids: Optional[torch.Tensor]
+    read: Optional[object]
+
+
 class Engine:
     def __init__(self, model_path: Optional[str], *, dtype: str = "auto", device: str = "cuda",
                  max_running_req: int = 256, max_seq_len: Optional[int] = None, page_size: int = 16,
                  memory_ratio: float = 0.9, max_total_tokens: Optional[int] = None,
                  max_prefill_tokens_per_batch: int = 8192, chunked_prefill_size: Optional[int] = None,
                  cuda_graph_bs: Optional[int] = 0, prefill_cuda_graph_max_tokens: int = 0,
-                 eos_token_ids: Optional[Sequence[int]] = None,
+                 eos_token_ids: Optional[Sequence[int]] = None, cpu_gpu_overlap: bool = True,
                  seed: int = 0, log_level: str = "info", random_weights_config: Optional[dict] = None,
                  random_weights_seed: int = 0):
         """``model_path``: a folder with config.json and model.safetensors.  With ``model_path`` None and
@@ -206,6 +214,9 @@ class Engine:
         self._scratch: Optional[torch.Tensor] = None
         self._params: Dict[int, SamplingParams] = {}
         self._seeds: Dict[int, int] = {}
+        self.cpu_gpu_overlap = bool(cpu_gpu_overlap)
+        self._flight: Optional[_Flight] = None          # the step that is already on the GPU (scheduler loop)
+        self.last_step_error = False
 
         self._graphs: Dict[int, _DecodeGraph] = {}
         if cuda_graph_bs is None:
@@ -428,41 +439,66 @@ class Engine:
     def is_idle(self) -> bool:
         return self.scheduler.is_idle()
 
+    def _launch(self, plan, relay: Optional[torch.Tensor]) -> "_Flight":
+        """Enqueue the forward pass and the sampling of ``plan`` and start the read-back of its tokens.
+        ``relay``: the token ids (on the device) that the step before sampled, in the order of ``plan``'s
+        entries, when those have not reached the host yet."""
+        sched = self.scheduler
+        entries, rows = [], []
+        for e in plan.entries:
+            tokens = [0] * e.count if relay is not None else sched.tokens_of(e)
+            entries.append(StepEntry(e.uid, tokens, [e.count - 1] if e.sample else []))
+            if e.sample:
+                rows.append((self._params[e.uid], self._seeds[e.uid], e.output_index))
+        logits = self.step(entries, device_tokens=relay)
+        if not rows:
+            return _Flight(plan, None, None)
+        ids = self.sampler.sample_device(logits, rows)
+        return _Flight(plan, ids, ops.begin_read(ids))
+
+    def _forget_finished(self, out) -> None:
+        for o in out:
+            if o.finished:
+                self._params.pop(o.uid, None)
+                self._seeds.pop(o.uid, None)
+
     def schedule_step(self):
-        """One scheduler step: plan, run, sample, commit.  Returns the step's output tokens."""
+        """One scheduler step: plan, run, sample, commit.  Returns the output tokens of one step.
+
+        With ``cpu_gpu_overlap`` the step after this one is put on the GPU before this one's tokens are
+        read, whenever the scheduler can name it without them (``Scheduler.successor``: one decoded token
+        for every running request, their inputs passed on the device); the host's work between two steps
+        then runs beside the GPU's.  A request that ends meanwhile stays in that step as a dead row."""
         sched = self.scheduler
         out = list(sched.drain_outbox())
-        plan = sched.plan_step()
-        out += sched.drain_outbox()
-        if not plan.entries:
-            return out
+        flight, self._flight = self._flight, None
         try:
-            entries, rows = [], []
-            for e in plan.entries:
-                entries.append(StepEntry(e.uid, sched.tokens_of(e), [e.count - 1] if e.sample else []))
-                if e.sample:
-                    rows.append((self._params[e.uid], self._seeds[e.uid], e.output_index))
-            logits = self.step(entries)
-            if rows:
-                sampled = ops.read_ids_and_check(self.sampler.sample_device(logits, rows))
+            if flight is None:
+                plan = sched.plan_step()
+                out += sched.drain_outbox()
+                if not plan.entries:
+                    return out
+                flight = _Flight(plan, None, None)            # (so that a failing launch fails this plan)
+                flight = self._launch(plan, None)
+            if self.cpu_gpu_overlap and flight.ids is not None:
+                following = sched.successor(flight.plan)
+                if following.entries:
+                    self._flight = self._launch(following, flight.ids)
+            if flight.read is not None:
+                sampled = flight.read.finish()
                 if any(i < 0 for i in sampled):
                     raise RuntimeError("sampling produced no valid token for a row (were the logits finite?)")
             else:
                 sampled = []
                 self.check_kernel_errors()
         except Exception:
-            out += sched.fail_step(plan)
+            self._flight = None                               # its requests are those of this step: they end here
+            out += sched.fail_step(flight.plan)
             self.last_step_error = True
-            for o in out:
-                if o.finished:
-                    self._params.pop(o.uid, None)
-                    self._seeds.pop(o.uid, None)
+            self._forget_finished(out)
             raise
-        out += sched.commit_step(plan, sampled)
-        for o in out:
-            if o.finished:
-                self._params.pop(o.uid, None)
-                self._seeds.pop(o.uid, None)
+        out += sched.commit_step(flight.plan, sampled)
+        self._forget_finished(out)
         return out
 
     def generate(self, prompts: Sequence[Sequence[int]],

@@ -101,25 +101,48 @@ def check_errors(device: torch.device) -> None:
 _staging = {}
 
 
-def read_ids_and_check(ids: torch.Tensor) -> list:
-    """Token ids (int32, on the device) as a host list, and the error word with them: two small copies into
-    pinned memory and ONE wait for the stream, instead of a blocking read each.  Raises as check_errors does."""
+class PendingRead:
+    """Token ids and the error word on their way to the host: ``begin_read`` enqueues the copies and an event,
+    ``finish`` waits for that event only, so kernels enqueued after ``begin_read`` keep the GPU busy meanwhile."""
+
+    def __init__(self, buf, n, event, device):
+        self.buf, self.n, self.event, self.device = buf, n, event, device
+
+    def finish(self) -> list:
+        self.event.synchronize()
+        value = int(self.buf[self.n])
+        if value:
+            error_word(self.device).zero_()
+            what = [text for bit, text in ERROR_BITS.items() if value & bit]
+            raise KernelError("a kernel refused an access: " + "; ".join(what))
+        return self.buf[:self.n].tolist()
+
+
+def begin_read(ids: torch.Tensor) -> PendingRead:
+    """Start copying ``ids`` (int32, on the device) and the error word into pinned memory (two small copies on
+    the current stream, then an event).  Four staging buffers per device take turns: at most three reads may be
+    pending when a fourth begins."""
     device = ids.device
     key = device.index or 0
     n = ids.numel()
-    buf = _staging.get(key)
-    if buf is None or buf.numel() < n + 1:
-        buf = _staging[key] = torch.empty(max(1024, 2 * (n + 1)), dtype=torch.int32).pin_memory()
-    word = error_word(device)
+    ring = _staging.get(key)
+    if ring is None or ring[0][0].numel() < n + 1:
+        size = max(1024, 2 * (n + 1))
+        ring = _staging[key] = ([torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(4)], [0])
+    bufs, turn = ring
+    buf = bufs[turn[0] % len(bufs)]
+    turn[0] += 1
     buf[:n].copy_(ids.reshape(-1), non_blocking=True)
-    buf[n:n + 1].copy_(word, non_blocking=True)
-    torch.cuda.current_stream(device).synchronize()
-    value = int(buf[n])
-    if value:
-        word.zero_()
-        what = [text for bit, text in ERROR_BITS.items() if value & bit]
-        raise KernelError("a kernel refused an access: " + "; ".join(what))
-    return buf[:n].tolist()
+    buf[n:n + 1].copy_(error_word(device), non_blocking=True)
+    event = torch.cuda.Event()
+    event.record(torch.cuda.current_stream(device))
+    return PendingRead(buf, n, event, device)
+
+
+def read_ids_and_check(ids: torch.Tensor) -> list:
+    """Token ids (int32, on the device) as a host list, and the error word with them: two small copies into
+    pinned memory and ONE wait, instead of a blocking read each.  Raises as check_errors does."""
+    return begin_read(ids).finish()
 
 
 # --------------------------------------------------------------------------- libraries

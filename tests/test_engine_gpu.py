@@ -264,3 +264,50 @@ def test_refusals_at_start_up_and_in_a_step(tiny, tiny_dirs, tmp_path):
     eng.step([StepEntry(1, [1, 2, 300], [])])                          # 300 is outside the vocabulary of 256
     with pytest.raises(Exception, match="token id"):
         eng.check_kernel_errors()
+
+
+@pytest.mark.parametrize("dtype,graphs", [("float32", 0), ("bfloat16", 4)])
+def test_steps_launched_ahead_give_the_same_tokens(dtype, graphs, tiny, tiny_dirs, tmp_path):
+    """With the next step put on the GPU before this step's tokens are read, every request gets the tokens it
+    gets with one step at a time: requests of different lengths, stop ids that end some of them while their
+    next step already runs, sampled and greedy rows, requests that arrive and are aborted in between."""
+    from llm_infer_rust_b200 import SamplingParams, write_random_model
+    v = tiny["B"]
+    folder = tiny_dirs["B"] if dtype == "float32" else \
+        write_random_model(str(tmp_path / "m"), v["raw"], v["seed"], norm_std=v["norm_std"], dtype="bfloat16")
+    prompts = [tokens(509, n, 70 + n) for n in (3, 11, 40, 7, 25, 2)]
+    params = [SamplingParams(max_tokens=m, temperature=t, seed=5 + i, ignore_eos=ig)
+              for i, (m, t, ig) in enumerate([(30, 0.0, False), (12, 0.9, False), (9, 0.0, True), (1, 0.0, False),
+                                              (40, 1.1, False), (17, 0.0, False)])]
+
+    def run(overlap, stops):
+        eng = engine(folder, dtype=dtype, page_size=v["page_size"], max_total_tokens=1024, max_running_req=4,
+                     cuda_graph_bs=graphs, eos_token_ids=stops, cpu_gpu_overlap=overlap)
+        got = eng.generate(prompts, params)
+        assert eng.cache.manager.live_requests() == 0 and eng.cache.manager.check() == ""
+        # requests that come and go while steps are in flight
+        uids = [eng.add_request(p, sp) for p, sp in zip(prompts[:3], params[:3])]
+        seen = {u: [] for u in uids}
+        steps = 0
+        while not eng.is_idle():
+            for o in eng.schedule_step():
+                if o.token >= 0:
+                    seen[o.uid].append(o.token)
+            steps += 1
+            if steps == 4:
+                assert eng.abort_request(uids[0])
+                uids.append(eng.add_request(prompts[4], params[4]))
+                seen[uids[-1]] = []
+        assert eng.cache.manager.live_requests() == 0 and eng.cache.manager.check() == ""
+        return [(r.tokens, r.finish_reason) for r in got], [seen[u] for u in uids]
+
+    serial, serial_loop = run(False, [])
+    # stop ids taken from what the requests really produce, so that some of them end early
+    stops = sorted({serial[0][0][5], serial[4][0][9], serial[5][0][3]})
+    for stop_ids in ([], stops):
+        a, a_loop = run(False, stop_ids)
+        b, b_loop = run(True, stop_ids)
+        assert a == b
+        assert a_loop[1:] == b_loop[1:]                       # (the aborted request may have got one token more or less)
+        assert b_loop[0] == a_loop[0][:len(b_loop[0])] or a_loop[0] == b_loop[0][:len(a_loop[0])]
+    assert any(reason == "stop" for _, reason in b) and any(reason == "length" for _, reason in b)

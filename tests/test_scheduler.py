@@ -198,3 +198,71 @@ def test_a_windowed_group_is_promised_less_and_never_runs_dry():
         if cache.has(a):
             assert cache.pages_held(a, 1) <= 4
     assert steps == 8 + 19 and cache.free_pages(1) == 16 and cache.free_pages(0) == 16
+
+
+# ---------------------------------------------------------------- a step planned before the one before it has reported
+def test_successor_is_one_decoded_token_for_every_request_in_the_plans_order():
+    cache, s = make(budget=32)
+    a = s.add_request([1, 2, 3], params(max_tokens=5))
+    b = s.add_request([4, 5], params(max_tokens=5))
+    plan = s.plan_step()                                     # both prompts whole, both sample
+    nxt = s.successor(plan)
+    assert [(e.uid, e.start, e.count, e.sample, e.output_index) for e in nxt.entries] == \
+        [(a, 3, 1, True, 1), (b, 2, 1, True, 1)] and nxt.decode_rows == 2
+    # what the scheduler plans after the commit is that very step
+    for e in plan.entries:
+        cache.grow(e.uid, e.start + e.count)
+        cache.advance(e.uid, e.start + e.count)
+    s.commit_step(plan, [50, 51])
+    assert shape(s.plan_step()) == [(a, 3, 1, True), (b, 2, 1, True)]
+
+
+def test_no_successor_when_a_decision_is_needed():
+    # somebody waits
+    cache, s = make(budget=4)
+    s.add_request([1, 2, 3, 4], params())
+    s.add_request([5, 6], params())
+    plan = s.plan_step()
+    assert s.num_pending() == 1 and not s.successor(plan).entries
+    # a prompt is not through yet
+    cache, s = make(budget=3)
+    s.add_request([1, 2, 3, 4, 5], params())
+    plan = s.plan_step()
+    assert shape(plan) == [(1, 0, 3, False)] and not s.successor(plan).entries
+    # a request ends by length with this step: max_tokens, then max_seq_len
+    cache, s = make()
+    s.add_request([1, 2], params(max_tokens=1))
+    assert not s.successor(s.plan_step()).entries
+    cache, s = make(max_seq=4)
+    s.add_request([1, 2, 3], params(max_tokens=9))
+    assert not s.successor(s.plan_step()).entries           # 3 prompt tokens + 1 output = max_seq_len
+    cache, s = make(max_seq=5)
+    s.add_request([1, 2, 3], params(max_tokens=9))
+    assert len(s.successor(s.plan_step()).entries) == 1
+
+
+def test_a_request_that_ends_while_its_successor_step_runs_is_a_dead_row():
+    cache, s = make(eos=[99])
+    a = s.add_request([1, 2], params(max_tokens=8))
+    b = s.add_request([3], params(max_tokens=8))
+    c = s.add_request([4, 5, 6], params(max_tokens=8))
+
+    def run(plan):
+        for e in plan.entries:
+            cache.grow(e.uid, e.start + e.count)
+            cache.advance(e.uid, e.start + e.count)
+
+    plan = s.plan_step()
+    run(plan)
+    nxt = s.successor(plan)
+    assert [e.uid for e in nxt.entries] == [a, b, c]
+    run(nxt)                                                 # the engine launches it before it knows plan's tokens
+    out = s.commit_step(plan, [10, 99, 12])                  # b draws the stop id
+    assert [(o.uid, o.token, o.finished) for o in out] == [(a, 10, False), (b, 99, True), (c, 12, False)]
+    assert s.abort_request(c)                                # and c is aborted meanwhile
+    out = s.commit_step(nxt, [20, 21, 22])                   # the tokens of b and c are dropped
+    assert [(o.uid, o.token) for o in out] == [(a, 20)]
+    assert shape(s.plan_step()) == [(a, 3, 1, True)]
+    with pytest.raises(ValueError):
+        s.commit_step(nxt, [20, 21])                         # still one token for every sampling row
+    assert cache.check() == ""
