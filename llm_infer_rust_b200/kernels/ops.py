@@ -493,6 +493,86 @@ def skinny_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int
     return True
 
 
+_tuned = {}
+_flush_buffers = {}
+TUNE_FROM_BYTES = 24 << 20              # weights from this size on are routed by measurement
+
+
+def _timed_cold(fn, device) -> float:
+    """Median time in ms of ``fn()`` with the L2 flushed before every run (weights come from HBM in a real step)."""
+    key = torch.device(device).index or 0
+    flush = _flush_buffers.get(key)
+    if flush is None:
+        flush = _flush_buffers[key] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    times = []
+    for it in range(7):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        end.synchronize()
+        if it >= 2:                                           # the first runs load the kernels
+            times.append(start.elapsed_time(end))
+    return sorted(times)[len(times) // 2]
+
+
+def few_row_pays(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
+                 head_dim: int = 0, fused_norm: bool = False) -> bool:
+    """Whether the few-row kernel (with the norm before it and the epilogue after it fused in) is the faster
+    way to this product than the library product with those as kernels of their own.
+
+    Small matrices (under TUNE_FROM_BYTES) always take the kernel: there launches decide and it has fewest.  For
+    larger ones it is measured, once per process for every (weight shape, epilogue, norm or not, 1 / up to 8 / up
+    to 16 rows): the kernel wins where the library's choice for the shape is poor, the library on some large
+    matrices (each CTA of the kernel normalises the rows itself and keeps its K-slice of them in shared memory).  During a graph capture nothing is measured (a capture is
+    preceded by a run of the same step outside it, which has asked already)."""
+    if not skinny_ok(rows, weight, act_dtype, mode, head_dim):
+        return False
+    bucket = 1 if rows == 1 else (8 if rows <= 8 else SKINNY_MAX_ROWS)
+    key = (weight.device.index or 0, weight.shape[0], weight.shape[1], mode, bool(fused_norm), bucket)
+    known = _tuned.get(key)
+    if known is not None:
+        return known
+    n, k = weight.shape
+    if torch.cuda.is_current_stream_capturing() or 2 * n * k < TUNE_FROM_BYTES:
+        return True
+    dev = weight.device
+    # the QKV epilogue needs a cache and positions: it is timed as the plain product, its library rival with
+    # one more small kernel (per-head norm, rotation, cache store), which at these row counts is launch time
+    kernel_mode = EPI_PLAIN_BF16 if mode == EPI_QKV else mode
+    if kernel_mode != mode and not skinny_ok(bucket, weight, act_dtype, kernel_mode):
+        _tuned[key] = True
+        return True
+    x = torch.randn(bucket, k, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    residual = torch.randn(bucket, k, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    norm_w = torch.ones(k, device=dev, dtype=torch.bfloat16)
+    scratch_res = residual.clone()
+
+    def fused():
+        skinny_linear(PendingNorm(x, residual, norm_w, 1e-6) if fused_norm else x, weight, kernel_mode)
+
+    def library():
+        y = x
+        if fused_norm:
+            y = add_rms_norm(x, scratch_res, norm_w, 1e-6)        # (the residual is updated in place, as in a step)
+        if mode == EPI_PLAIN_F32:
+            torch.mm(y, weight.t(), out_dtype=torch.float32)
+            return
+        z = torch.mm(y, weight.t())
+        if mode == EPI_SWIGLU or (mode == EPI_QKV and n % 2 == 0):
+            silu_mul(z)                                       # (QKV: stands in for the small kernel after the product)
+
+    before = launch_count()
+    t_fused, t_library = _timed_cold(fused, dev), _timed_cold(library, dev)
+    add_launches(before - launch_count())                     # measurements are not the model's launches
+    # Measured alone, the kernel is charged a launch that it does not pay inside a step: launched with programmatic
+    # dependent launch it sets up and fetches weights under the tail of the kernel before it.  The library must win
+    # by more than that.
+    _tuned[key] = t_fused <= t_library + 0.0015
+    return _tuned[key]
+
+
 def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
                   qkv: Optional[dict] = None) -> torch.Tensor:
     """epilogue(prologue(x) . weight^T) for at most 16 rows, in one kernel.
@@ -651,7 +731,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         _cuda(x, weight)
         if out_dtype in (torch.bfloat16, torch.float32) and x.dim() == 2 and x.is_contiguous() \
-                and skinny_ok(x.shape[0], weight, x.dtype):
+                and few_row_pays(x.shape[0], weight, x.dtype,
+                                 EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16):
             return skinny_linear(x, weight, EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16)
         if out_dtype == torch.bfloat16:
             return torch.mm(x, weight.t())

@@ -77,7 +77,7 @@ class GQAttention(Part):
 
     def takes_pending(self, tokens: int) -> bool:
         """Whether a step of ``tokens`` tokens runs the input norm as the prologue of the QKV product."""
-        return ops.skinny_ok(tokens, self.params["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d)
+        return ops.few_row_pays(tokens, self.params["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d, fused_norm=True)
 
     def forward(self, x, ctx, cache):
         p = self.params
@@ -85,7 +85,8 @@ class GQAttention(Part):
         rope = self.rope
         q = torch.empty((tokens, self.nh * self.d), dtype=x.dtype, device=x.device)
         slots = ctx.slots[cache.group] if cache.writes else None
-        if self.takes_pending(tokens):
+        if ops.few_row_pays(tokens, p["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d,
+                            fused_norm=isinstance(x, ops.PendingNorm)):
             # few tokens: norm (if pending), projection, per-head norm, rotation and cache store in one kernel
             ops.skinny_linear(x, p["qkv_proj"], ops.EPI_QKV, qkv=dict(
                 head_dim=self.d, num_heads=self.nh, num_kv_heads=self.nkv, q_out=q, k_cache=cache.k, v_cache=cache.v,

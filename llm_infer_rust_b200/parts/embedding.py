@@ -41,7 +41,7 @@ class LinearHead(Part):
         return {"weight": ParamDecl((self.vocab, self.hidden))}
 
     def takes_pending(self, rows: int) -> bool:
-        return ops.skinny_ok(rows, self.params["weight"], self.env.dtype, ops.EPI_PLAIN_F32)
+        return ops.few_row_pays(rows, self.params["weight"], self.env.dtype, ops.EPI_PLAIN_F32, fused_norm=True)
 
     def forward(self, x):
         if isinstance(x, ops.PendingNorm):

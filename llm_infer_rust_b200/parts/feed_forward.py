@@ -25,10 +25,11 @@ class SwiGLU(Part):
 
     def takes_pending(self, tokens: int) -> bool:
         """Whether a step of ``tokens`` tokens runs the norm before it as the prologue of the gate/up product."""
-        return ops.skinny_ok(tokens, self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU)
+        return ops.few_row_pays(tokens, self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU, fused_norm=True)
 
     def forward(self, x):
-        if self.takes_pending(x.shape[0]):
+        if ops.few_row_pays(x.shape[0], self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU,
+                            fused_norm=isinstance(x, ops.PendingNorm)):
             # few tokens: norm (if pending), gate and up projections and silu(gate) * up in one kernel
             return ops.linear(ops.skinny_linear(x, self.params["gate_up_proj"], ops.EPI_SWIGLU), self.params["down_proj"])
         if isinstance(x, ops.PendingNorm):
