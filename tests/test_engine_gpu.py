@@ -311,3 +311,58 @@ def test_steps_launched_ahead_give_the_same_tokens(dtype, graphs, tiny, tiny_dir
         assert a_loop[1:] == b_loop[1:]                       # (the aborted request may have got one token more or less)
         assert b_loop[0] == a_loop[0][:len(b_loop[0])] or a_loop[0] == b_loop[0][:len(a_loop[0])]
     assert any(reason == "stop" for _, reason in b) and any(reason == "length" for _, reason in b)
+
+
+def test_many_requests_arriving_and_ending_at_random_with_and_without_steps_ahead(tiny, tiny_dirs):
+    """Sixty requests of random lengths arrive between steps, some are aborted, stop ids end others: with steps
+    launched ahead every request that was not aborted gets the tokens it gets one step at a time, and the cache
+    ends empty both ways."""
+    import random
+    from llm_infer_rust_b200 import SamplingParams
+    v = tiny["A"]
+    vocab = v["raw"]["vocab_size"]
+
+    def run(overlap):
+        rnd = random.Random(7)
+        eng = engine(tiny_dirs["A"], dtype="float32", page_size=v["page_size"], max_total_tokens=640,
+                     max_running_req=6, max_seq_len=100, eos_token_ids=[3, 17, 101, 200], cpu_gpu_overlap=overlap)
+        todo = [(tokens(vocab, rnd.randint(1, 40), 300 + i),
+                 SamplingParams(max_tokens=rnd.randint(1, 30), temperature=rnd.choice([0.0, 0.0, 0.8]), seed=i,
+                                ignore_eos=rnd.random() < 0.3)) for i in range(60)]
+        abort_at = {i: rnd.randint(1, 12) for i in rnd.sample(range(60), 8)}    # request -> steps after its arrival
+        results, uid_of, age, aborted = {}, {}, {}, set()
+        step = 0
+        while todo or not eng.is_idle():
+            for _ in range(rnd.randint(0, 2)):
+                if todo:
+                    i = 60 - len(todo)
+                    prompt, sp = todo.pop(0)
+                    uid_of[i] = eng.add_request(prompt, sp)
+                    results[uid_of[i]] = ([], None)
+                    age[i] = 0
+            for o in eng.schedule_step():
+                toks, _ = results[o.uid]
+                if o.token >= 0:
+                    toks.append(o.token)
+                if o.finished:
+                    results[o.uid] = (toks, o.reason.name)
+            for i in list(age):
+                age[i] += 1
+                if abort_at.get(i) == age[i] and results[uid_of[i]][1] is None:
+                    eng.abort_request(uid_of[i])
+                    aborted.add(i)
+            step += 1
+            assert step < 5000
+        assert eng.cache.manager.live_requests() == 0 and eng.cache.manager.check() == ""
+        return {i: results[u] for i, u in uid_of.items()}, aborted
+
+    serial, aborted_a = run(False)
+    ahead, aborted_b = run(True)
+    assert len(serial) == len(ahead) == 60
+    reasons = set()
+    for i in range(60):
+        if i in aborted_a or i in aborted_b:
+            continue                                          # an aborted request may be a token further one way
+        assert serial[i] == ahead[i], i
+        reasons.add(serial[i][1])
+    assert {"Stop", "Length"} <= reasons
