@@ -5,16 +5,16 @@
 //   S = Q K^T      tcgen05.mma, M 128, N 128 (keys), K 16 x 8; Q and K are K-major tiles in the 128-byte swizzle
 //                  (Q is written there by the softmax warps, K arrives by TMA); S lands in one of TWO score
 //                  buffers in tensor memory, so the scores of block i + 1 are computed under the softmax of block i;
-//   softmax        eight warps, two threads per query row with 64 keys each: the scores come into registers once
-//                  (tcgen05.ld), the two threads exchange their maxima through shared memory, then exp2 and the
-//                  row sum; the bfloat16 probabilities go back into tensor memory (tcgen05.st), two to a column,
-//                  over the first half of the scores they came from;
+//   softmax        four warps, one thread per query row: two passes over the row of S in tensor memory
+//                  (tcgen05.ld): the row maximum, then exp2 and the row sum; the bfloat16 probabilities go back
+//                  into tensor memory (tcgen05.st), two to a column, over the first half of the scores they
+//                  came from;
 //   O += P V       tcgen05.mma with the A operand in tensor memory, M 128, N 128 (head dims), K 16 x 8,
 //                  accumulating in tensor memory over all blocks; V is used as it lies in the cache (keys x dims,
 //                  the dims contiguous: an MN-major B operand).  The tensor pipe runs the MMAs of one thread in
 //                  the order of issue, so the scores of block i + 2 overwrite the buffer only behind P V of block i.
 //                  The probabilities are taken relative to a reference maximum that is raised only when a row's
-//                  maximum has grown by more than 2^8 (then the row's two threads rescale its O in tensor memory,
+//                  maximum has grown by more than 2^8 (then the row's thread rescales its O in tensor memory,
 //                  tcgen05.ld / st, once P V of the block before is finished); a stale reference is exact, since
 //                  the row sum uses the same one.
 // One warp fetches K blocks (ring of three) and V blocks (ring of two) by TMA; one warp owns tensor memory and
@@ -40,15 +40,15 @@ constexpr int BKV = 128;                 // keys per block
 constexpr int HALF = BKV * 128;          // bytes of a [128 rows x 64 columns] half tile
 constexpr int TILE = 2 * HALF;           // bytes of a [128 x 128] bfloat16 tile
 constexpr int K_STAGES = 3, V_STAGES = 2;
-constexpr int THREADS = 320;             // warp 0: copies, warp 1: MMA, warps 2-9: softmax (two threads per query row)
+constexpr int THREADS = 192;             // one tile per CTA: warp 0 copies, warp 1 MMA, warps 2-5 softmax
+constexpr int PAIR_THREADS = 320;        // two tiles per CTA: four more softmax warps
 constexpr int TMEM_COLS = 512;           // S buffers (and P in their first 64 columns): columns 0..127 and 128..255; O: 256..383
 constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only growth beyond 2^8
 
-// Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers and the softmax threads' exchange.
+// Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers.
 constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, BAR_OFF = Q_OFF + TILE;
-constexpr int N_BARS = 2 * K_STAGES + 2 * V_STAGES + 2 + 4 + 4;
-constexpr int XCH_OFF = BAR_OFF + (N_BARS + 1) * 8;      // (one more slot holds the tensor-memory address)
-constexpr int SMEM_BYTES = XCH_OFF + 2 * 2 * 128 * 4;
+constexpr int N_BARS = 2 * K_STAGES + 2 * V_STAGES + 2 + 4;
+constexpr int SMEM_BYTES = BAR_OFF + (N_BARS + 1) * 8;      // (one more slot holds the tensor-memory address)
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
@@ -163,6 +163,143 @@ __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.
 // Byte offset of (row r, 16-byte chunk c of 16) inside a [128 x 128] bfloat16 tile of two swizzled halves.
 __device__ __forceinline__ int swz(int r, int c) { return (c >> 3) * HALF + r * 128 + (((c & 7) ^ (r & 7)) << 4); }
 
+// ---------------------------------------------------------------------------------------------------------------
+// What the softmax threads of both kernels do.  A thread owns one query row: lane r of tensor memory.
+
+// The row's Q vector into its K-major tile in the 128-byte swizzle (zeros for a row that is not used).
+__device__ __forceinline__ void write_q_row(unsigned char* q_tile, const bf16* src, int r, bool used) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (used) v = *reinterpret_cast<const uint4*>(src + c * 8);
+    *reinterpret_cast<uint4*>(q_tile + swz(r, c)) = v;
+  }
+  proxy_fence();
+}
+
+// Row r of an MN-major value tile (128 dims in two halves of 128 bytes), set to zero.
+__device__ __forceinline__ void zero_value_row(unsigned char* v_tile, int r) {
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(v_tile + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
+}
+
+struct RowState {
+  float m_ref = -INFINITY;     // reference maximum (log2 units): follows the row's maximum in steps of RESCALE_STEP
+  float l_run = 0.0f;          // sum of the probabilities relative to it
+};
+
+// One block of 128 keys for this thread's row.  The scores lie in the 128 columns from s_base on; the bfloat16
+// probabilities go back over the first 64 of them, two to a column (the A operand of P V), and are in tensor memory
+// when the function returns.  `block` counts the row's blocks from 0; P V of block - 1 commits to `pv_done`.  Every
+// phase of that barrier is waited for here, in order: before the accumulator at o_base is rescaled (the row's
+// maximum grew by more than the step), else at the end, when that product has long finished.  A wait by parity
+// cannot tell "phase b - 1 is not finished" from "phase b - 2 is not finished": a waiter that skipped a phase
+// would pass at once.  Returns false when a wait ran out.
+__device__ __forceinline__ bool softmax_block(uint32_t s_base, uint32_t o_base, int first_key, int qpos, int kv_end,
+                                              int window, bool masked, float scale_log2, int block, uint64_t* pv_done,
+                                              RowState& st, int* err) {
+  tc_fence_after();
+  // pass 1: the row's maximum over the block's visible keys (of the raw scores; the scale is positive)
+  float mx = -INFINITY;
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    float v[64];
+    tmem_ld64(s_base + c * 64, v);
+    if (masked) {
+#pragma unroll
+      for (int e = 0; e < 64; ++e) {
+        const int key = first_key + c * 64 + e;
+        const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+        mx = fmaxf(mx, vis ? v[e] : -INFINITY);
+      }
+    } else {
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
+#pragma unroll
+      for (int e = 0; e < 64; e += 4) {
+        m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
+      }
+      mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+    }
+  }
+  mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
+  // The reference follows the maximum when it grew by more than the step (or there was none yet).
+  const bool raise = mx > st.m_ref + RESCALE_STEP || (st.m_ref == -INFINITY && mx > -INFINITY);
+  const float m_new = raise ? mx : st.m_ref;
+  const float corr = raise ? (st.m_ref == -INFINITY ? 0.0f : exp2f(st.m_ref - m_new)) : 1.0f;
+  const float base = m_new == -INFINITY ? 0.0f : m_new;
+  bool pv_seen = block == 0;
+  // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
+  if (block > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
+    if (!mbar_wait_warp(pv_done, (block - 1) & 1, err)) return false;
+    pv_seen = true;
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float o[32];
+      tmem_ld32(o_base + c * 32, o);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) o[e] *= corr;
+      tmem_st32(o_base + c * 32, o);
+    }
+  }
+  st.l_run = st.l_run * corr;
+  st.m_ref = m_new;
+  // pass 2: probabilities relative to the reference and their sum; those of columns 64c .. 64c + 63 go back into
+  // tensor memory over the scores that were just read (columns 32c .. 32c + 31)
+  const float neg_base = qpos >= 0 ? -base : -INFINITY;      // a row that is not used gets zeros
+  float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    float v[64];
+    tmem_ld64(s_base + c * 64, v);
+    if (masked) {
+#pragma unroll
+      for (int e = 0; e < 64; ++e) {
+        const int key = first_key + c * 64 + e;
+        const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
+        v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
+    }
+    uint32_t pr[32];
+#pragma unroll
+    for (int e = 0; e < 64; e += 2) {
+      sum4[(e >> 1) & 3] += v[e] + v[e + 1];
+      __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
+      pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
+    }
+    tmem_st32_raw(s_base + c * 32, pr);
+  }
+  st.l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+  tmem_wait_st();                                      // P is in tensor memory
+  return pv_seen || mbar_wait_warp(pv_done, (block - 1) & 1, err);
+}
+
+// The finished row: the accumulator over the row's sum, as bfloat16.  (Every lane of the warp takes part in the
+// loads, also those whose row is not used.)
+__device__ __forceinline__ void store_output(uint32_t o_base, bf16* dst, float l_run, bool used) {
+  tc_fence_after();
+  const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float o[32];
+    tmem_ld32(o_base + c * 32, o);
+    if (used) {
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        __align__(16) bf16 y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[q4 * 8 + e] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = *reinterpret_cast<const uint4*>(y);
+      }
+    }
+  }
+  tc_fence_before();
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                        const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
@@ -179,8 +316,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   uint64_t* q_full = s_full + 2;
   uint64_t* p_full = q_full + 1;                                     // [2]: one per score buffer, so that a softmax that runs
   uint64_t* pv_done = p_full + 2;                                    //      a block ahead can never lap the MMA thread's wait
-  uint64_t* pair_bar = pv_done + 1;                                  // [4]: the two softmax warps of each quarter
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -188,11 +324,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
     mbar_init(s_full, 1);
     mbar_init(s_full + 1, 1);
-    mbar_init(q_full, 8);
-    mbar_init(p_full, 8);
-    mbar_init(p_full + 1, 8);
+    mbar_init(q_full, 4);
+    mbar_init(p_full, 4);
+    mbar_init(p_full + 1, 4);
     mbar_init(pv_done, 1);
-    for (int w = 0; w < 4; ++w) mbar_init(pair_bar + w, 2);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -299,157 +434,41 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       }
     }
   } else {
-    // ---- softmax warps: two threads per query row.  Warps 2-5 take the first 64 keys of every block, warps 6-9
-    // the last 64; warp w reaches the tensor-memory lanes 32 (w mod 4) .. + 31, so the warps w and w + 4 share
-    // their rows.  The two threads of a row exchange their maxima (and at the end their sums) through shared
-    // memory and a barrier of their own.
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    // ---- softmax warps: thread r owns query row r of the tile (tensor-memory lane r)
+    const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int tok = r / group, head = head0 + r % group;
     const bool used = tok < ntok;
     const int qpos = used ? p_lo + tok : -1;
-    float* xch = reinterpret_cast<float*>(sm + XCH_OFF);          // [2 parities][2 halves][128 rows]
-    uint64_t* pair = pair_bar + quarter;
     if (nblk > 0) {
-      // Q row into its swizzled K-major tile (zeros for an unused row), eight chunks by each of the two threads
-      const bf16* src = q + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
-#pragma unroll
-      for (int c = half * 8; c < half * 8 + 8; ++c) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (used) v = *reinterpret_cast<const uint4*>(src + c * 8);
-        *reinterpret_cast<uint4*>(sm + Q_OFF + swz(r, c)) = v;
-      }
-      proxy_fence();
+      write_q_row(sm + Q_OFF, q + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D, r, used);
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
     }
-    float m_ref = -INFINITY, l_run = 0.0f;             // reference maximum (log2 units) and this thread's part of the row sum
+    RowState st;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
-    for (int i = 0; i < nblk; ++i) {
-      const int blk_first = k_begin + i * BKV;
-      const int first_key = blk_first + half * 64;     // of this thread's 64 keys
-      const uint32_t s_base = lane_base + (i & 1) * 128;
+    for (int i = 0; i < nblk && ok; ++i) {
+      const int first_key = k_begin + i * BKV;
       if (!mbar_wait_warp(s_full + (i & 1), (i >> 1) & 1, err)) { ok = false; break; }
-      tc_fence_after();
-      const bool masked = blk_first + BKV - 1 > p_lo || blk_first + BKV > kv_end || (window > 0 && blk_first <= p_lo + ntok - 1 - window);
-      // this thread's 64 scores stay in registers from here to the probabilities
-      float v[64];
-      tmem_ld64(s_base + half * 64, v);
-      float mx = -INFINITY;
-      if (masked) {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          const int key = first_key + e;
-          const bool vis = key <= qpos && key < kv_end && (window <= 0 || key > qpos - window);
-          v[e] = vis ? v[e] : -INFINITY;
-          mx = fmaxf(mx, v[e]);
-        }
-      } else {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one
-#pragma unroll
-        for (int e = 0; e < 64; e += 4) {
-          m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
-        }
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      }
-      // The row's maximum over both halves.  Past this barrier both threads have read their scores, so the
-      // probabilities may overwrite them.
-      xch[((i & 1) * 2 + half) * 128 + r] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pair);
-      if (!mbar_wait_warp(pair, i & 1, err)) { ok = false; break; }
-      mx = fmaxf(mx, xch[((i & 1) * 2 + (half ^ 1)) * 128 + r]);
-      mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
-      // The reference follows the maximum when it grew by more than the step (or there was none yet).
-      const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
-      const float m_new = raise ? mx : m_ref;
-      const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
-      const float base = m_new == -INFINITY ? 0.0f : m_new;
-      // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
-      // (Both warps of a pair see the same rows and maxima, so they decide alike; each takes 64 of the columns.)
-      bool pv_seen = i == 0;                             // whether this block has looked at P V of the block before
-      if (i > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
-        if (!mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
-        pv_seen = true;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          float o[32];
-          tmem_ld32(lane_base + 256 + half * 64 + c * 32, o);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] *= corr;
-          tmem_st32(lane_base + 256 + half * 64 + c * 32, o);
-        }
-      }
-      l_run = l_run * corr;
-      m_ref = m_new;
-      // Probabilities relative to the reference and their sum.  The bfloat16 probabilities of this thread's 64 keys
-      // go back into tensor memory, two to a column (columns 32 half .. + 31 of this score buffer): the A operand
-      // of P V.  The buffer's next scores are issued behind that product.  (A hidden score is -inf and gives 0.)
-      const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
-#pragma unroll
-      for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      uint32_t pr[32];
-#pragma unroll
-      for (int e = 0; e < 64; e += 2) {
-        sum4[(e >> 1) & 3] += v[e] + v[e + 1];
-        __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
-        pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
-      }
-      tmem_st32_raw(s_base + half * 32, pr);
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      const bool masked = first_key + BKV - 1 > p_lo || first_key + BKV > kv_end || (window > 0 && first_key <= p_lo + ntok - 1 - window);
+      ok = softmax_block(lane_base + (i & 1) * 128, lane_base + 256, first_key, qpos, kv_end, window, masked, scale_log2, i,
+                         pv_done, st, err);
       // value rows beyond what the tile may see must not reach P V, whatever the page or the stage held
-      if (blk_first + BKV > kv_end) {
+      if (ok && first_key + BKV > kv_end) {
         const int s = i % V_STAGES;
-        if (!mbar_wait_warp(v_full + s, (i / V_STAGES) & 1, err)) { ok = false; break; }      // the copies have landed
-        if (blk_first + r >= kv_end) {
-          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-          for (int c = half * 8; c < half * 8 + 8; ++c)
-            *reinterpret_cast<uint4*>(sm + V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
-        }
-        proxy_fence();                                 // the zeroed rows are visible to the tensor cores
+        ok = mbar_wait_warp(v_full + s, (i / V_STAGES) & 1, err);      // the copies have landed
+        if (ok && first_key + r >= kv_end) zero_value_row(sm + V_OFF + s * TILE, r);
+        proxy_fence();                                                 // the zeroed rows are visible to the tensor cores
       }
-      tmem_wait_st();                                  // P is in tensor memory
-      // Every phase of pv_done is waited for, in order: a wait by parity cannot tell "phase i - 1 is not finished"
-      // from "phase i - 2 is not finished", and a waiter two phases ahead would pass at once.  Here, at the end of
-      // the block's work, P V of the block before has long finished.
-      if (!pv_seen && !mbar_wait_warp(pv_done, (i - 1) & 1, err)) { ok = false; break; }
+      if (!ok) break;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + (i & 1));
     }
-    if (ok && nblk > 0) {
-      // the row sum over both halves
-      xch[((nblk & 1) * 2 + half) * 128 + r] = l_run;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pair);
-      ok = mbar_wait_warp(pair, nblk & 1, err);
-      if (ok) l_run += xch[((nblk & 1) * 2 + (half ^ 1)) * 128 + r];
-    }
     if (ok && nblk > 0) ok = mbar_wait_warp(pv_done, (nblk - 1) & 1, err);
-    if (ok && nblk > 0) {
-      tc_fence_after();
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      bf16* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D + half * 64;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float o[32];
-        tmem_ld32(lane_base + 256 + half * 64 + c * 32, o);      // (every lane of the warp takes part in the load)
-        if (used) {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            __align__(16) bf16 y[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[q4 * 8 + e] * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = *reinterpret_cast<const uint4*>(y);
-          }
-        }
-      }
-      tc_fence_before();
-    }
+    if (ok && nblk > 0)
+      store_output(lane_base + 256, out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D, st.l_run, used);
   }
   tc_fence_before();
   __syncthreads();
@@ -475,7 +494,7 @@ constexpr int PAIR_BAR_OFF = PAIR_Q_OFF + 2 * TILE;
 constexpr int PAIR_N_BARS = 2 * PAIR_K_STAGES + 2 * PAIR_V_STAGES + 2 + 2 + 2 + 1;
 constexpr int PAIR_SMEM_BYTES = PAIR_BAR_OFF + (PAIR_N_BARS + 1) * 8;
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                             const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
@@ -625,142 +644,37 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
     const bool used = tok < my_ntok;
     const int qpos = used ? my_p_lo + tok : -1;
     if (nblk_all > 0) {
-      // Q row into its tile (zeros for an unused row, and for all rows of a tile without tokens)
-      const bf16* src = q + (static_cast<size_t>(q_begin + my_tok0 + tok) * nh + head) * D;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (used) v = *reinterpret_cast<const uint4*>(src + c * 8);
-        *reinterpret_cast<uint4*>(sm + PAIR_Q_OFF + t * TILE + swz(r, c)) = v;
-      }
-      proxy_fence();
+      // (zeros for an unused row, and for all rows of a tile without tokens)
+      write_q_row(sm + PAIR_Q_OFF + t * TILE, q + (static_cast<size_t>(q_begin + my_tok0 + tok) * nh + head) * D, r, used);
       __syncwarp();
       if (lane == 0) mbar_arrive(q_full);
     }
-    float m_ref = -INFINITY, l_run = 0.0f;
+    RowState st;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_base = lane_base + t * 128, o_base = lane_base + 256 + t * 128;
     bool ok = true;
-    for (int b = 0; b < my_blocks; ++b) {
+    for (int b = 0; b < my_blocks && ok; ++b) {
       const int first_key = k_begin + b * BKV;
       if (!mbar_wait_warp(s_full + t, b & 1, err)) { ok = false; break; }
-      tc_fence_after();
       const bool masked = first_key + BKV - 1 > my_p_lo || first_key + BKV > my_kv_end ||
                           (window > 0 && first_key <= my_p_lo + my_ntok - 1 - window);
-      // pass 1: the row's maximum over the block's visible keys (of the raw scores; the scale is positive)
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[64];
-        tmem_ld64(s_base + c * 64, v);
-        if (masked) {
-#pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int key = first_key + c * 64 + e;
-            const bool vis = key <= qpos && key < my_kv_end && (window <= 0 || key > qpos - window);
-            mx = fmaxf(mx, vis ? v[e] : -INFINITY);
-          }
-        } else {
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int e = 0; e < 64; e += 4) {
-            m4[0] = fmaxf(m4[0], v[e]); m4[1] = fmaxf(m4[1], v[e + 1]); m4[2] = fmaxf(m4[2], v[e + 2]); m4[3] = fmaxf(m4[3], v[e + 3]);
-          }
-          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-        }
-      }
-      mx = qpos >= 0 ? mx * scale_log2 : -INFINITY;
-      const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
-      const float m_new = raise ? mx : m_ref;
-      const float corr = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new)) : 1.0f;
-      const float base = m_new == -INFINITY ? 0.0f : m_new;
-      // The accumulator may be rescaled only between two products: P V of the block before has to be finished.
-      bool pv_seen = b == 0;                             // whether this block has looked at P V of the block before
-      if (b > 0 && __any_sync(0xffffffffu, raise ? 1 : 0)) {
-        if (!mbar_wait_warp(pv_done + t, (b - 1) & 1, err)) { ok = false; break; }
-        pv_seen = true;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float o[32];
-          tmem_ld32(o_base + c * 32, o);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] *= corr;
-          tmem_st32(o_base + c * 32, o);
-        }
-      }
-      l_run = l_run * corr;
-      m_ref = m_new;
-      // pass 2: probabilities relative to the reference and their sum; the bfloat16 probabilities of columns
-      // 64c .. 64c + 63 go back into tensor memory over the scores just read (columns 32c .. 32c + 31).
-      const float neg_base = qpos >= 0 ? -base : -INFINITY;      // an unused row gets zeros
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[64];
-        tmem_ld64(s_base + c * 64, v);
-        if (masked) {
-#pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int key = first_key + c * 64 + e;
-            const bool vis = key <= qpos && key < my_kv_end && (window <= 0 || key > qpos - window);
-            v[e] = vis ? fast_exp2(fmaf(v[e], scale_log2, neg_base)) : 0.0f;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 64; ++e) v[e] = fast_exp2(fmaf(v[e], scale_log2, neg_base));
-        }
-        uint32_t pr[32];
-#pragma unroll
-        for (int e = 0; e < 64; e += 2) {
-          sum4[(e >> 1) & 3] += v[e] + v[e + 1];
-          __nv_bfloat162 two = __floats2bfloat162_rn(v[e], v[e + 1]);
-          pr[e >> 1] = *reinterpret_cast<uint32_t*>(&two);
-        }
-        tmem_st32_raw(s_base + c * 32, pr);
-      }
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      ok = softmax_block(s_base, o_base, first_key, qpos, my_kv_end, window, masked, scale_log2, b, pv_done + t, st, err);
       // Value rows beyond what the CTA may see must not reach P V, whatever the page or the stage held.  Both tiles
       // write the same zeros, each before its own product.
-      if (first_key + BKV > kv_end_all) {
+      if (ok && first_key + BKV > kv_end_all) {
         const int s = b % VS;
-        if (!mbar_wait_warp(v_full + s, (b / VS) & 1, err)) { ok = false; break; }
-        if (first_key + r >= kv_end_all) {
-          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-          for (int c = 0; c < 16; ++c)
-            *reinterpret_cast<uint4*>(sm + PAIR_V_OFF + s * TILE + (c >> 3) * HALF + r * 128 + (c & 7) * 16) = zero;
-        }
+        ok = mbar_wait_warp(v_full + s, (b / VS) & 1, err);
+        if (ok && first_key + r >= kv_end_all) zero_value_row(sm + PAIR_V_OFF + s * TILE, r);
         proxy_fence();
       }
-      tmem_wait_st();
-      // every phase of pv_done is waited for, in order (see the kernel above)
-      if (!pv_seen && !mbar_wait_warp(pv_done + t, (b - 1) & 1, err)) { ok = false; break; }
+      if (!ok) break;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + t);
     }
     if (ok && my_blocks > 0) ok = mbar_wait_warp(pv_done + t, (my_blocks - 1) & 1, err);
-    if (ok && my_blocks > 0) {
-      tc_fence_after();
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      bf16* dst = out + (static_cast<size_t>(q_begin + my_tok0 + tok) * nh + head) * D;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float o[32];
-        tmem_ld32(o_base + c * 32, o);
-        if (used) {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            __align__(16) bf16 y[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = __float2bfloat16_rn(o[q4 * 8 + e] * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = *reinterpret_cast<const uint4*>(y);
-          }
-        }
-      }
-      tc_fence_before();
-    }
+    if (ok && my_blocks > 0)
+      store_output(o_base, out + (static_cast<size_t>(q_begin + my_tok0 + tok) * nh + head) * D, st.l_run, used);
   }
   tc_fence_before();
   __syncthreads();
@@ -819,7 +733,7 @@ B200_EXPORT int b200_prefill_attention_tcgen05(const void* q, const void* k_map,
   if (n_rows > 65535 || n_tiles > 65535) return B200_BAD_SIZE;      // the grid's y and z extents
   dim3 grid(nkv, n_rows, n_tiles);
   ++g_launches[pairs ? 1 : 0];
-  return b200_launch(pairs ? prefill_tcgen05_pair_kernel : prefill_tcgen05_kernel, grid, dim3(THREADS), smem, stream, 0, kmap,
+  return b200_launch(pairs ? prefill_tcgen05_pair_kernel : prefill_tcgen05_kernel, grid, dim3(pairs ? PAIR_THREADS : THREADS), smem, stream, 0, kmap,
                      vmap, static_cast<const bf16*>(q), static_cast<bf16*>(out), block_table, table_stride, cu_q, kv_len,
                      prefix_len, rows, nh, nkv, page_size, box_rows, window, scale * 1.4426950408889634f, err);
 }
