@@ -9,6 +9,8 @@ src/layers/linear.rs:5-7); everything else is this package's own code.
 from __future__ import annotations
 
 import ctypes
+import os
+import sys
 from typing import Optional
 
 import torch
@@ -499,22 +501,30 @@ TUNE_FROM_BYTES = 24 << 20              # weights from this size on are routed b
 
 
 def _timed_cold(fn, device) -> float:
-    """Median time in ms of ``fn()`` with the L2 flushed before every run (weights come from HBM in a real step)."""
+    """Median time in ms of ``fn()`` replayed as a CUDA graph (as it will run inside a step: the library chooses
+    other kernels under capture than in eager mode) with the L2 flushed before every run (weights come from HBM in
+    a real step)."""
     key = torch.device(device).index or 0
     flush = _flush_buffers.get(key)
     if flush is None:
         flush = _flush_buffers[key] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    fn()
+    fn()                                                      # loads the kernels, sets the library up
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
     times = []
-    for it in range(7):
+    for _ in range(6):
         flush.zero_()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        fn()
+        graph.replay()
         end.record()
         end.synchronize()
-        if it >= 2:                                           # the first runs load the kernels
-            times.append(start.elapsed_time(end))
-    return sorted(times)[len(times) // 2]
+        times.append(start.elapsed_time(end))
+    del graph
+    return sorted(times[1:])[len(times) // 2 - 1]
 
 
 def few_row_pays(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
@@ -522,8 +532,8 @@ def few_row_pays(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: 
     """Whether the few-row kernel (with the norm before it and the epilogue after it fused in) is the faster
     way to this product than the library product with those as kernels of their own.
 
-    Small matrices (under TUNE_FROM_BYTES) always take the kernel: there launches decide and it has fewest.  For
-    larger ones it is measured, once per process for every (weight shape, epilogue, norm or not, 1 / up to 8 / up
+    Small matrices (under TUNE_FROM_BYTES) and float32 results (the head) always take the kernel: there launches
+    decide and it has fewest.  For larger ones it is measured, once per process for every (weight shape, epilogue, norm or not, 1 / up to 8 / up
     to 16 rows): the kernel wins where the library's choice for the shape is poor, the library on some large
     matrices (each CTA of the kernel normalises the rows itself and keeps its K-slice of them in shared memory).  During a graph capture nothing is measured (a capture is
     preceded by a run of the same step outside it, which has asked already)."""
@@ -535,7 +545,11 @@ def few_row_pays(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: 
     if known is not None:
         return known
     n, k = weight.shape
-    if torch.cuda.is_current_stream_capturing() or 2 * n * k < TUNE_FROM_BYTES:
+    # Not measured: small matrices; the head (once a step; given to the library, 64 us against 81 us for the product
+    # at the 0.6B shape, a prefill step of 255 kernels took 0.1 ms LONGER, all of it in gaps between other kernels:
+    # a measurement of one product does not see what another kind of node does to the rest of a step's graph, and
+    # only the layers' products of large models are worth that risk).
+    if torch.cuda.is_current_stream_capturing() or 2 * n * k < TUNE_FROM_BYTES or mode == EPI_PLAIN_F32:
         return True
     dev = weight.device
     # the QKV epilogue needs a cache and positions: it is timed as the plain product, its library rival with
@@ -570,6 +584,10 @@ def few_row_pays(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: 
     # dependent launch it sets up and fetches weights under the tail of the kernel before it.  The library must win
     # by more than that.
     _tuned[key] = t_fused <= t_library + 0.0015
+    if os.environ.get("LLM_INFER_B200_LOG_ROUTING"):
+        print(f"[llm_infer_rust_b200] few-row product {n} x {k}, epilogue {mode}, norm {int(fused_norm)}, up to {bucket} "
+              f"rows: kernel {t_fused * 1e3:.1f} us, library {t_library * 1e3:.1f} us -> "
+              f"{'kernel' if _tuned[key] else 'library'}", file=sys.stderr, flush=True)
     return _tuned[key]
 
 
