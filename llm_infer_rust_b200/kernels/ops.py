@@ -141,12 +141,6 @@ def begin_read(ids: torch.Tensor) -> PendingRead:
     return PendingRead(buf, n, event, device)
 
 
-def read_ids_and_check(ids: torch.Tensor) -> list:
-    """Token ids (int32, on the device) as a host list, and the error word with them: two small copies into
-    pinned memory and ONE wait, instead of a blocking read each.  Raises as check_errors does."""
-    return begin_read(ids).finish()
-
-
 # --------------------------------------------------------------------------- libraries
 def _elementwise():
     return load_cuda_library("elementwise.cu")
