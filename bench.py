@@ -10,9 +10,11 @@ decoded greedily, and the last K steps are timed.  One JSON line is printed:
 
 * ``value``: decoded tokens a second, timed on the device (CUDA events around K steps that are
   queued back to back: each step's sampled tokens go to the next step on the device);
-* ``e2e``: the same through ``Engine.add_request`` / ``Engine.schedule_step``: token ids go in
-  from the host, every step's index arrays are copied from pinned host memory and its sampled
-  ids are read back;
+* ``e2e``: the same through ``Engine.add_request`` / ``Engine.schedule_step``: prompts go in as
+  host token ids, every step's index arrays are copied from pinned host memory, its sampled ids
+  are read back to the host and returned to the caller step by step (the scheduler loop launches
+  the next decode step before it has read the running one's ids, so a decoded token reaches the
+  next step on the device as well as the host);
 * ``prefill``: one step of 2,048 prompt tokens; ``frac`` = its FLOPs / time / the bfloat16 peak;
 * ``roofline``: bytes that a decode step must read (every weight once and the cache of the live
   requests) / its time, against the measured copy bandwidth;
