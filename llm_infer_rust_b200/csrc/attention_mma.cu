@@ -230,8 +230,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
   if (threadIdx.x < WARPS * STAGES) mbar_init(bars + threadIdx.x, 1);
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  __syncthreads();
   pdl_launch_dependents();
-  pdl_wait();                      // the step's index arrays, q and the newest keys and values come from earlier kernels
+  // The kernel before this one in the stream wrote q and the step's newest key and value of every row.  The
+  // step's index arrays were uploaded before the step's first kernel, and all other keys and values are older:
+  // both may be read while that kernel still runs.
   const int splits = gridDim.x, split = blockIdx.x, kvh = blockIdx.y;
   const int row = rows[blockIdx.z];
   const int group = nh / nkv, head0 = kvh * group;
@@ -246,6 +249,30 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
   const int* table = block_table + static_cast<size_t>(row) * table_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
+  unsigned char* my = tiles + static_cast<size_t>(warp) * STAGES * TILE_BYTES;
+  uint64_t* my_bars = bars + warp * STAGES;
+  int issue = blk_lo + warp;
+  int page = 0;
+  auto first_fill = [&]() {                            // the ring's first STAGES - 1 blocks of this warp
+    page = issue < blk_hi ? lane_page(table, page_size, box_rows, k_begin + issue * KB, kv_end, lane) : 0;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      const int next = issue + WARPS;
+      const int next_page = next < blk_hi ? lane_page(table, page_size, box_rows, k_begin + next * KB, kv_end, lane) : 0;
+      if (issue < blk_hi)
+        fetch_block(my + s * TILE_BYTES, &kmap, &vmap, page, page_size, nkv, kvh, box_rows, k_begin + issue * KB, kv_end,
+                    my_bars + s, lane);
+      issue = next;
+      page = next_page;
+    }
+  };
+  // They are fetched under the tail of the kernel before, unless the newest key (position kv_end - 1) is in them.
+  const int last_of_fill = blk_lo + warp + (STAGES - 2) * WARPS;
+  const bool early = k_begin + (last_of_fill + 1) * KB <= qp;
+  if (early) first_fill();
+  pdl_wait();
+  if (!early) first_fill();
+
   for (int c = threadIdx.x; c < QROWS * (D / 8); c += blockDim.x) {
     const int r = c / (D / 8), part = c - r * (D / 8);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -255,23 +282,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
   __syncthreads();
   const int g = lane >> 2;
   const int qpos0 = g < group ? qp : -1, qpos1 = g + 8 < group ? qp : -1;
-
-  unsigned char* my = tiles + static_cast<size_t>(warp) * STAGES * TILE_BYTES;
-  uint64_t* my_bars = bars + warp * STAGES;
   WarpAcc st;
   st.init();
-  int issue = blk_lo + warp;
-  int page = issue < blk_hi ? lane_page(table, page_size, box_rows, k_begin + issue * KB, kv_end, lane) : 0;
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    const int next = issue + WARPS;
-    const int next_page = next < blk_hi ? lane_page(table, page_size, box_rows, k_begin + next * KB, kv_end, lane) : 0;
-    if (issue < blk_hi)
-      fetch_block(my + s * TILE_BYTES, &kmap, &vmap, page, page_size, nkv, kvh, box_rows, k_begin + issue * KB, kv_end,
-                  my_bars + s, lane);
-    issue = next;
-    page = next_page;
-  }
   int stage = 0;
   uint32_t parity = 0;
   for (int blk = blk_lo + warp; blk < blk_hi; blk += WARPS) {
