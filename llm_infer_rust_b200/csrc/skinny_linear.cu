@@ -154,6 +154,29 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   if (feeder && lane == 0)
     for (int j = 0; j < STAGES && j < nkb; ++j) issue(j);
   pdl_launch_dependents();
+  // What the QKV epilogue needs of the step's index arrays and of the rotary tables does not depend on the kernels
+  // before either: warp m fetches row m's position, cache slot and angles now, not at the end of the kernel, where
+  // two dependent loads would stand between the product and the store.
+  constexpr int ROT_PER_LANE = BN / 64;              // a head of BN dims rotates at most BN / 2 pairs: 32 lanes x BN / 64
+  int epi_pos = 0, epi_slot = 0;
+  float epi_cos[ROT_PER_LANE], epi_sin[ROT_PER_LANE];
+  bool epi_rotate = false;
+  if (p.mode == EPI_QKV && warp < p.M) {
+    if (p.slots != nullptr) epi_slot = p.slots[warp];
+    const int half = p.rot_dim / 2;
+    if (p.cos_table != nullptr && half > 0) {
+      epi_pos = p.positions[warp];
+      epi_rotate = epi_pos >= 0 && epi_pos < p.max_pos;
+      if (epi_rotate) {
+#pragma unroll
+        for (int j = 0; j < ROT_PER_LANE; ++j) {
+          const int i = lane + 32 * j;
+          epi_cos[j] = i < half ? p.cos_table[static_cast<size_t>(epi_pos) * half + i] : 1.0f;
+          epi_sin[j] = i < half ? p.sin_table[static_cast<size_t>(epi_pos) * half + i] : 0.0f;
+        }
+      }
+    }
+  }
   pdl_wait();                      // x, the residual and the cache belong to the kernels before this one
 
   // ---- prologue: the rows of x' for columns [k_lo, k_lo + kc) as bfloat16 in shared memory
@@ -333,54 +356,54 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
     constexpr int d = BN;
     const int head = tile;
     const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
-    for (int m = warp; m < M; m += WARPS + 1) {
+    static_assert(MMAX <= WARPS + 1, "one warp per row in the QKV epilogue");
+    if (warp < M) {
+      const int m = warp;                                                    // (its position, slot and angles were fetched at the start)
       float* row = red + m * (BN + 1);
       // the projection's output is a bfloat16 tensor in the unfused path; the same rounding here
       for (int i = lane; i < d; i += 32) row[i] = __bfloat162float(__float2bfloat16_rn(row[i]));
       __syncwarp();
-      bf16* dst;
+      bf16* dst = nullptr;
       if (is_q) {
         dst = static_cast<bf16*>(p.out) + (static_cast<size_t>(m) * p.nh + head) * d;
-      } else {
-        if (p.slots == nullptr) continue;
-        const int slot = p.slots[m];
-        if (slot == 0) continue;
-        if (slot < 0 || slot >= p.cache_slots) { if (lane == 0) atomicOr(p.err, B200_ERR_SLOT_RANGE); continue; }
-        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
-        const int page = slot / p.page_size, offset = slot - page * p.page_size;
-        dst = (is_k ? p.k_cache : p.v_cache) + ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + offset) * d;
-      }
-      if (!is_q && !is_k) {
-        for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
-        continue;
-      }
-      const void* w = is_q ? p.q_w : p.k_w;
-      if (w != nullptr) {
-        float ss = 0.0f;
-        for (int i = lane; i < d; i += 32) ss += row[i] * row[i];
-        ss = warp_sum(ss);
-        const float scale = rsqrtf(ss / static_cast<float>(d) + p.qk_eps);
-        for (int i = lane; i < d; i += 32) row[i] = row[i] * scale * norm_weight(w, p.qk_w_f32, i);
-        __syncwarp();
-      }
-      const int half = p.rot_dim / 2;
-      bool rotate = p.cos_table != nullptr && half > 0;
-      int pos = 0;
-      if (rotate) {
-        pos = p.positions[m];
-        if (pos < 0 || pos >= p.max_pos) { if (lane == 0) atomicOr(p.err, B200_ERR_POSITION_RANGE); rotate = false; }
-      }
-      if (rotate) {
-        const float* c = p.cos_table + static_cast<size_t>(pos) * half;
-        const float* s = p.sin_table + static_cast<size_t>(pos) * half;
-        for (int i = lane; i < half; i += 32) {
-          const float a = row[i], b = row[i + half];
-          dst[i] = __float2bfloat16_rn(a * c[i] - b * s[i]);
-          dst[i + half] = __float2bfloat16_rn(b * c[i] + a * s[i]);
+      } else if (p.slots != nullptr && epi_slot != 0) {
+        if (epi_slot < 0 || epi_slot >= p.cache_slots) {
+          if (lane == 0) atomicOr(p.err, B200_ERR_SLOT_RANGE);
+        } else {
+          const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+          const int page = epi_slot / p.page_size, offset = epi_slot - page * p.page_size;
+          dst = (is_k ? p.k_cache : p.v_cache) + ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + offset) * d;
         }
-        for (int i = p.rot_dim + lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
-      } else {
+      }
+      if (dst != nullptr && !is_q && !is_k) {
         for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
+      } else if (dst != nullptr) {
+        const void* w = is_q ? p.q_w : p.k_w;
+        if (w != nullptr) {
+          float ss = 0.0f;
+          for (int i = lane; i < d; i += 32) ss += row[i] * row[i];
+          ss = warp_sum(ss);
+          const float scale = rsqrtf(ss / static_cast<float>(d) + p.qk_eps);
+          for (int i = lane; i < d; i += 32) row[i] = row[i] * scale * norm_weight(w, p.qk_w_f32, i);
+          __syncwarp();
+        }
+        const int half = p.rot_dim / 2;
+        const bool wanted = p.cos_table != nullptr && half > 0;
+        if (wanted && !epi_rotate && lane == 0) atomicOr(p.err, B200_ERR_POSITION_RANGE);
+        if (wanted && epi_rotate) {
+#pragma unroll
+          for (int j = 0; j < ROT_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half) {
+              const float a = row[i], b = row[i + half];
+              dst[i] = __float2bfloat16_rn(a * epi_cos[j] - b * epi_sin[j]);
+              dst[i + half] = __float2bfloat16_rn(b * epi_cos[j] + a * epi_sin[j]);
+            }
+          }
+          for (int i = p.rot_dim + lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
+        } else {
+          for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(row[i]);
+        }
       }
     }
   }
