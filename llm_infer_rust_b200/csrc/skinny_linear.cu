@@ -118,6 +118,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   uint64_t* empty = full + STAGES;
   float* row_scale = reinterpret_cast<float*>(empty + STAGES);                 // [MMAX]
 
+  pdl_launch_dependents();         // the kernel after this one may set itself up from now on (it waits before it reads)
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = static_cast<int>(cluster.block_rank());
   const int tile = blockIdx.x / p.ksplit;
@@ -153,7 +154,6 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   const bool feeder = warp == WARPS;
   if (feeder && lane == 0)
     for (int j = 0; j < STAGES && j < nkb; ++j) issue(j);
-  pdl_launch_dependents();
   // What the QKV epilogue needs of the step's index arrays and of the rotary tables does not depend on the kernels
   // before either: warp m fetches row m's position, cache slot and angles now, not at the end of the kernel, where
   // two dependent loads would stand between the product and the store.

@@ -380,7 +380,8 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
             _p(q), kv_tensor_map(k_cache, box_rows), kv_tensor_map(v_cache, box_rows), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
             _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
             ctypes.c_float(scale), splits, _p(error_word(q.device)), _stream())
-        _ok(rc, "decode_attention_mma", 2 if splits > 1 else 1)
+        in_kernel = splits == 1 or (splits in (2, 4, 8) and splits * num_kv_heads * n_rows <= _sm_count(q.device))
+        _ok(rc, "decode_attention_mma", 1 if in_kernel else 2)      # (a cluster of 2, 4 or 8 splits combines them itself)
         return
     rc = _attention(head_dim).b200_decode_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
