@@ -177,6 +177,18 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
       }
     }
   }
+  // The norm's weights for the columns that this lane takes in the first pass over a row (the only pass up to 1,024
+  // columns): the same for every row and not written by the kernels before, so they are fetched ahead of the wait.
+  // Widened to 32-bit here: kept packed, the loads were found to be scheduled after the wait.
+  float first_w[4][8];
+  if (p.residual != nullptr) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = (u * 32 + lane) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) first_w[u][i] = k + i < K ? norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f;
+    }
+  }
   pdl_wait();                      // x, the residual and the cache belong to the kernels before this one
 
   // ---- prologue: the rows of x' for columns [k_lo, k_lo + kc) as bfloat16 in shared memory
@@ -227,7 +239,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
             __align__(16) bf16 weighted[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              weighted[i] = __float2bfloat16_rn(k < K ? sum[i] * norm_weight(p.norm_w, p.norm_w_f32, k + i) : 0.0f);
+              weighted[i] = __float2bfloat16_rn(k >= K ? 0.0f : sum[i] * (k0 == 0 ? first_w[u][i] : norm_weight(p.norm_w, p.norm_w_f32, k + i)));
             *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(weighted);
           }
         }
