@@ -48,7 +48,9 @@ constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only g
 // Shared memory: V stages, K stages, Q (each tile 32 KB), then the barriers.
 constexpr int V_OFF = 0, K_OFF = V_STAGES * TILE, Q_OFF = K_OFF + K_STAGES * TILE, BAR_OFF = Q_OFF + TILE;
 constexpr int N_BARS = 2 * K_STAGES + 2 * V_STAGES + 2 + 4;
-constexpr int SMEM_BYTES = BAR_OFF + (N_BARS + 1) * 8;      // (one more slot holds the tensor-memory address)
+constexpr int TBL_ENTRIES = 2048;         // page numbers of a row that the copy warp keeps in shared memory (the rest it reads as before)
+constexpr int TBL_OFF = BAR_OFF + (N_BARS + 1) * 8;      // (one more slot holds the tensor-memory address)
+constexpr int SMEM_BYTES = TBL_OFF + TBL_ENTRIES * 4;
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
@@ -364,7 +366,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     // ---- copies: lane j fetches the sub-blocks j, j + 32, ... (box_rows keys each) of a block of 128 keys.
     // Keys run one block further ahead than values (three stages against two): S of block i + 2 is wanted
     // while block i is still in the softmax.
+    // The row's page numbers for this tile's keys come into shared memory first: a copy then does not begin with a
+    // load from global memory whose answer it needs for its address.
     bool ok = true;
+    int* tbl = reinterpret_cast<int*>(sm + TBL_OFF);
+    const int first_page = k_begin / page_size;
+    const int n_pages = min(TBL_ENTRIES, (kv_end + page_size - 1) / page_size - first_page);
+    for (int t = lane; t < n_pages; t += 32) tbl[t] = table[first_page + t];
+    __syncwarp();
     auto fetch = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int first_key) {
       const int n_sub = (min(BKV, kv_end - first_key) + box_rows - 1) / box_rows;
       proxy_fence();
@@ -372,7 +381,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       __syncwarp();
       for (int j = lane; j < n_sub; j += 32) {
         const int key0 = first_key + j * box_rows;
-        const int page = table[key0 / page_size];
+        const int pi = key0 / page_size - first_page;
+        const int page = pi < TBL_ENTRIES ? tbl[pi] : table[first_page + pi];
         const int y = (page * nkv + kvh) * page_size + key0 % page_size;
         tma_load_2d(dst + j * box_rows * 128, map, 0, y, bar);
         tma_load_2d(dst + HALF + j * box_rows * 128, map, 64, y, bar);
@@ -492,7 +502,8 @@ constexpr int PAIR_K_STAGES = 2, PAIR_V_STAGES = 2;      // (deeper rings were s
 constexpr int PAIR_V_OFF = 0, PAIR_K_OFF = PAIR_V_STAGES * TILE, PAIR_Q_OFF = PAIR_K_OFF + PAIR_K_STAGES * TILE;
 constexpr int PAIR_BAR_OFF = PAIR_Q_OFF + 2 * TILE;
 constexpr int PAIR_N_BARS = 2 * PAIR_K_STAGES + 2 * PAIR_V_STAGES + 2 + 2 + 2 + 1;
-constexpr int PAIR_SMEM_BYTES = PAIR_BAR_OFF + (PAIR_N_BARS + 1) * 8;
+constexpr int PAIR_TBL_OFF = PAIR_BAR_OFF + (PAIR_N_BARS + 1) * 8;
+constexpr int PAIR_SMEM_BYTES = PAIR_TBL_OFF + TBL_ENTRIES * 4;
 
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -561,6 +572,11 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
   if (warp == 0) {
     // ---- copies, as in the kernel above
     bool ok = true;
+    int* tbl = reinterpret_cast<int*>(sm + PAIR_TBL_OFF);
+    const int first_page = k_begin / page_size;
+    const int n_pages = min(TBL_ENTRIES, (kv_end_all + page_size - 1) / page_size - first_page);
+    for (int t = lane; t < n_pages; t += 32) tbl[t] = table[first_page + t];
+    __syncwarp();
     auto fetch = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int first_key) {
       const int n_sub = (min(BKV, kv_end_all - first_key) + box_rows - 1) / box_rows;
       proxy_fence();
@@ -568,7 +584,8 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
       __syncwarp();
       for (int j = lane; j < n_sub; j += 32) {
         const int key0 = first_key + j * box_rows;
-        const int page = table[key0 / page_size];
+        const int pi = key0 / page_size - first_page;
+        const int page = pi < TBL_ENTRIES ? tbl[pi] : table[first_page + pi];
         const int y = (page * nkv + kvh) * page_size + key0 % page_size;
         tma_load_2d(dst + j * box_rows * 128, map, 0, y, bar);
         tma_load_2d(dst + HALF + j * box_rows * 128, map, 64, y, bar);
