@@ -13,12 +13,10 @@ all go through it.
 """
 from __future__ import annotations
 
-import os
 from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
-import numpy as np
 import torch
 
 from .. import architectures  # noqa: F401  (registers the shipped architectures)

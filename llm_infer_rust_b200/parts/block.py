@@ -2,7 +2,6 @@
 from __future__ import annotations
 
 from .registry import build_part, register_part
-from ..config.spec import PartSpec
 
 
 class PreNormDeferredAdd:

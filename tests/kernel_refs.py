@@ -8,7 +8,6 @@ code with the package.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

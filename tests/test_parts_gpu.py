@@ -2,7 +2,6 @@
 plain implementation's function for the same part."""
 import math
 
-import numpy as np
 import pytest
 import torch
 
