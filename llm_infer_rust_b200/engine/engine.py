@@ -377,7 +377,7 @@ class Engine:
             torch.cuda.synchronize(self.device)
             g.graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(g.graph):
+            with ops.graph_capture(g.graph):
                 g.logits = self.model.forward(g.ctx, self.cache.layer_caches)
             g.launches = ops.launch_count() - before
             ops.add_launches(-g.launches)        # captured, not run

@@ -8,7 +8,9 @@ src/layers/linear.rs:5-7); everything else is this package's own code.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import gc
 import os
 import sys
 from typing import Optional
@@ -496,6 +498,25 @@ _flush_buffers = {}
 TUNE_FROM_BYTES = 24 << 20              # weights from this size on are routed by measurement
 
 
+@contextlib.contextmanager
+def graph_capture(graph: "torch.cuda.CUDAGraph"):
+    """Capture the stream's work into ``graph``.
+
+    Python's cycle collector runs first and is held off until the capture has ended.  A dead reference cycle that
+    owns CUDA graphs or device memory (an engine that the caller dropped, say) is else freed at whatever allocation
+    inside the capture happens to start a collection; destroying a graph or returning its memory is not permitted
+    while a stream captures, and the capture ends with "operation failed due to a previous error during capture"."""
+    gc.collect()
+    held = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if held:
+            gc.enable()
+
+
 def _timed_cold(fn, device) -> float:
     """Median time in ms of ``fn()`` replayed as a CUDA graph (as it will run inside a step: the library chooses
     other kernels under capture than in eager mode) with the L2 flushed before every run (weights come from HBM in
@@ -508,7 +529,7 @@ def _timed_cold(fn, device) -> float:
     fn()                                                      # loads the kernels, sets the library up
     torch.cuda.synchronize(device)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    with graph_capture(graph):
         fn()
     times = []
     for _ in range(6):

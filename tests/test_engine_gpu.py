@@ -366,3 +366,40 @@ def test_many_requests_arriving_and_ending_at_random_with_and_without_steps_ahea
         assert serial[i] == ahead[i], i
         reasons.add(serial[i][1])
     assert {"Stop", "Length"} <= reasons
+
+
+def test_a_dropped_engine_in_a_dead_cycle_does_not_break_the_next_capture(tiny, tmp_path):
+    """An engine that was dropped while a reference cycle still held it is freed by Python's cycle collector, at
+    whatever allocation starts a collection.  Inside a graph capture that would destroy CUDA graphs and return
+    their memory, which a capturing stream does not permit: the capture collects first and holds the collector
+    off.  Here the collector is off until the second engine's capture, where the model's forward pass (wrapped)
+    asks for a collection in the middle of it."""
+    import gc
+    from llm_infer_rust_b200 import SamplingParams, write_random_model
+    v = tiny["B"]
+    folder = write_random_model(str(tmp_path / "m"), v["raw"], v["seed"], norm_std=v["norm_std"], dtype="bfloat16")
+    prompts = [tokens(509, n, 30 + n) for n in (5, 9)]
+    params = [SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)] * 2
+    common = dict(dtype="bfloat16", page_size=v["page_size"], max_total_tokens=512, max_running_req=2)
+    want = [r.tokens for r in engine(folder, cuda_graph_bs=0, **common).generate(prompts, params)]
+    gc.collect()
+    gc.disable()
+    try:
+        first = engine(folder, cuda_graph_bs=2, **common)
+        assert [r.tokens for r in first.generate(prompts, params)] == want       # (its decode graphs exist now)
+        ring = [first]
+        ring.append(ring)
+        del first, ring                                       # unreachable; only the cycle collector can free it
+        second = engine(folder, cuda_graph_bs=2, **common)
+        forward, collected = second.model.forward, []
+
+        def collecting_forward(*args, **kwargs):
+            if torch.cuda.is_current_stream_capturing():
+                collected.append(gc.collect())
+            return forward(*args, **kwargs)
+
+        second.model.forward = collecting_forward
+        assert [r.tokens for r in second.generate(prompts, params)] == want
+        assert collected, "no decode graph was captured"
+    finally:
+        gc.enable()
