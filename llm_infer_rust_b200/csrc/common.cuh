@@ -82,6 +82,26 @@ template <> struct Vec16<__nv_bfloat16> {
   }
 };
 
+// N consecutive elements of T as floats, fetched with 16-byte loads (8-byte for four bfloat16): N * sizeof(T) is 8,
+// 16 or 32 bytes and p is aligned to the load's size.
+template <typename T, int N>
+__device__ __forceinline__ void load_floats(const T* p, float* out) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(p + i);
+      out[i] = v.x; out[i + 1] = v.y; out[i + 2] = v.z; out[i + 3] = v.w;
+    }
+  } else if constexpr (N == 8) {
+    Vec16<T>::load(p, out);
+  } else {
+    static_assert(N == 4, "four or eight elements");
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
+    out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+}
+
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   // Copies 16 bytes, or writes 16 zero bytes when !valid (src-size 0).
   uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));

@@ -91,8 +91,10 @@ rms_norm_warp_kernel(TA* out, const TA* x, TA* residual, const TW* __restrict__ 
     const int c = (i * 32 + lane) * N;
     if (i * 32 + lane < vectors) {
       __align__(16) TA y[N];
+      float wv[N];
+      load_floats<TW, N>(w + c, wv);
 #pragma unroll
-      for (int e = 0; e < N; ++e) y[e] = from_f32<TA>(v[i][e] * scale * to_f32<TW>(w[c + e]));
+      for (int e = 0; e < N; ++e) y[e] = from_f32<TA>(v[i][e] * scale * wv[e]);
       *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(y);
     }
   }
@@ -112,21 +114,43 @@ __global__ void silu_mul_kernel(TA* __restrict__ out, const TA* __restrict__ gat
 }
 
 // The same with 16-byte loads and stores: `width` is a multiple of the vector length and the pointers are aligned.
+// A thread takes two vectors a turn, with all four loads in flight before the arithmetic.  bfloat16 results take
+// the fast exponential and division (their error is far below the rounding to 8 bits); float32 takes the exact ones.
 template <typename TA>
-__global__ void silu_mul_vec_kernel(TA* __restrict__ out, const TA* __restrict__ gate_up, int width, size_t vectors) {
+__device__ __forceinline__ float silu_times(float g, float u) {
+  if constexpr (sizeof(TA) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
+  else return g / (1.0f + expf(-g)) * u;
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+silu_mul_vec_kernel(TA* __restrict__ out, const TA* __restrict__ gate_up, int width, size_t vectors) {
   constexpr int N = Vec16<TA>::N;
   const int per_row = width / N;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < vectors;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t row = i / per_row;
-    const int col = static_cast<int>(i - row * per_row) * N;
-    float g[N], u[N];
-    Vec16<TA>::load(gate_up + row * 2 * width + col, g);
-    Vec16<TA>::load(gate_up + row * 2 * width + width + col, u);
-    __align__(16) TA r[N];
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < vectors; i0 += 2 * stride) {
+    float g[2][N], u[2][N];
+    size_t dst[2];
 #pragma unroll
-    for (int e = 0; e < N; ++e) r[e] = from_f32<TA>(g[e] / (1.0f + expf(-g[e])) * u[e]);
-    *reinterpret_cast<uint4*>(out + row * width + col) = *reinterpret_cast<const uint4*>(r);
+    for (int j = 0; j < 2; ++j) {
+      const size_t i = i0 + j * stride;
+      if (i < vectors) {
+        const size_t row = i / per_row;
+        const int col = static_cast<int>(i - row * per_row) * N;
+        Vec16<TA>::load(gate_up + row * 2 * width + col, g[j]);
+        Vec16<TA>::load(gate_up + row * 2 * width + width + col, u[j]);
+        dst[j] = row * width + col;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (i0 + j * stride < vectors) {
+        __align__(16) TA r[N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) r[e] = from_f32<TA>(silu_times<TA>(g[j][e], u[j][e]));
+        *reinterpret_cast<uint4*>(out + dst[j]) = *reinterpret_cast<const uint4*>(r);
+      }
+    }
   }
 }
 
@@ -165,7 +189,7 @@ B200_EXPORT int b200_rms_norm(void* out, const void* x, void* residual, const vo
     // The warp-per-row kernel where it applies (16-byte aligned rows of at most 32 * 4 vectors).
     const int vec = act_dtype == B200_F32 ? 4 : 8;
     const bool aligned = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
-                         reinterpret_cast<uintptr_t>(residual) % 16 == 0;
+                         reinterpret_cast<uintptr_t>(residual) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
     if (width % vec == 0 && width / vec <= 32 * 16 && aligned) {
       const int blocks = (n_rows + 7) / 8;
       const bool small = width / vec <= 32 * 4;
@@ -211,7 +235,7 @@ B200_EXPORT int b200_silu_mul(void* out, const void* gate_up, int tokens, int wi
   const int vec = act_dtype == B200_F32 ? 4 : 8;
   if (width % vec == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0) {
     const size_t vectors = total / vec;
-    const int vblocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (vectors + 255) / 256));
+    const int vblocks = static_cast<int>(min(static_cast<size_t>(148 * 16), (vectors + 511) / 512));
     if (act_dtype == B200_F32)
       silu_mul_vec_kernel<float><<<vblocks, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up),
                                                               width, vectors);

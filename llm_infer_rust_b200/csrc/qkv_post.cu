@@ -142,8 +142,10 @@ qkv_post_vec_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out, TA* __re
   const TW* w = is_q ? q_w : k_w;
   if ((is_q || is_k) && w != nullptr) {
     const float scale = rsqrtf(ss / static_cast<float>(d) + eps);
+    float wv[N];
+    load_floats<TW, N>(w + sub * N, wv);
 #pragma unroll
-    for (int e = 0; e < N; ++e) v[e] = v[e] * scale * to_f32<TW>(w[sub * N + e]);
+    for (int e = 0; e < N; ++e) v[e] = v[e] * scale * wv[e];
   }
   const int half_lanes = lanes >> 1;
   float partner[N];
@@ -156,8 +158,9 @@ qkv_post_vec_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out, TA* __re
     } else {
       const bool first = sub < half_lanes;
       const int ci = (first ? sub : sub - half_lanes) * N;
-      const float* c = cos_table + static_cast<size_t>(pos) * (d / 2) + ci;
-      const float* sn = sin_table + static_cast<size_t>(pos) * (d / 2) + ci;
+      float c[N], sn[N];                                      // (one wide load each: a lane's N angles are contiguous)
+      load_floats<float, N>(cos_table + static_cast<size_t>(pos) * (d / 2) + ci, c);
+      load_floats<float, N>(sin_table + static_cast<size_t>(pos) * (d / 2) + ci, sn);
 #pragma unroll
       for (int e = 0; e < N; ++e) v[e] = first ? v[e] * c[e] - partner[e] * sn[e] : v[e] * c[e] + partner[e] * sn[e];
     }
@@ -183,7 +186,9 @@ B200_EXPORT int b200_qkv_post(const void* qkv, void* q_out, void* k_cache, void*
     const int vec = act_dtype == B200_F32 ? 4 : 8;
     const int lanes = d % vec == 0 ? d / vec : 0;
     const bool aligned = reinterpret_cast<uintptr_t>(qkv) % 16 == 0 && reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
-                         reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0;
+                         reinterpret_cast<uintptr_t>(k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(q_w) % 16 == 0 && reinterpret_cast<uintptr_t>(k_w) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(cos_table) % 16 == 0 && reinterpret_cast<uintptr_t>(sin_table) % 16 == 0;
     const bool whole_rotation = cos_table == nullptr || rot_dim == d;
     if (lanes >= 2 && lanes <= 32 && (lanes & (lanes - 1)) == 0 && aligned && whole_rotation) {
       const long long threads = work * lanes;
