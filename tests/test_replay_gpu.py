@@ -126,6 +126,24 @@ def test_mixed_with_pages_used_again(name, dtype, tiny, tiny_weights, tiny_dirs,
         check(np.concatenate(got[r]), want[r], dtype, f"request {r} of the mixed run")
 
 
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_a_checkpoint_stored_in_32_bit_under_the_bfloat16_engine(name, tiny, tiny_weights, tiny_dirs, tmp_path):
+    """A tensor stored in 32-bit stays so: with a float32 folder the bfloat16 engine keeps every weight in float32
+    (the products widen the bfloat16 activations), and the logits are those of the float32 weights within the
+    bfloat16 engine's bound."""
+    raw, page = tiny[name]["raw"], tiny[name]["page_size"]
+    vocab, T = raw["vocab_size"], LENGTHS[name]
+    ids = tokens(vocab, T, 12)
+    want = oracle(tiny_weights[name], raw, ids, "float32")
+    rp = Replay(tiny_dirs[name], "bfloat16", 2 * T, str(tmp_path / "out"), vocab, ["--page-size", str(page)])
+    try:
+        check(run_alone(rp, "whole", ids, [T]), want, "bfloat16", "whole")
+        check(run_alone(rp, "decoded", ids, [T - 32] + [1] * 32), want, "bfloat16", "last 32 decoded")
+        check(run_alone(rp, "portions", ids, [2, 17, 3, 64, T - 86]), want, "bfloat16", "portions")
+    finally:
+        assert rp.close() == 0
+
+
 def test_replay_refuses_what_it_cannot_hold(tiny, tiny_dirs, tmp_path):
     raw = tiny["A"]["raw"]
     rp = Replay(tiny_dirs["A"], "float32", 64, str(tmp_path / "out"), raw["vocab_size"], ["--page-size", "4"])
