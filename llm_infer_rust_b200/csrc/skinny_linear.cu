@@ -453,10 +453,12 @@ B200_EXPORT int b200_weight_tensor_map(void* out_map, const void* weight, long l
   return 0;
 }
 
-// Rows of the weight tile that a CTA owns: QKV: the head size (64, 128 or 256; 0: refused); else 128.
+// Rows of the weight tile that a CTA owns: QKV: the head size (64, 128 or 256; 0: refused); else 128, or 256 for
+// a matrix of so many rows (a vocabulary) that tiles of 256 still make four waves of CTAs: every CTA normalises
+// the rows of x and fills its ring once, whatever its tile's size.
 B200_EXPORT int b200_skinny_tile_rows(int mode, int head_dim, int n, int sm_count) {
-  (void)n; (void)sm_count;
   if (mode == EPI_QKV) return (head_dim == 64 || head_dim == 128 || head_dim == 256) ? head_dim : 0;
+  if (mode != EPI_SWIGLU && n >= 4 * 256 * (sm_count > 0 ? sm_count : 148)) return 256;
   return 128;
 }
 

@@ -134,7 +134,8 @@ def _bf(t):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (5, 509, 96), (8, 1000, 1024), (13, 130, 3000), (16, 256, 2048),
-                                   (3, 96, 12288), (16, 64, 12288), (2, 4000, 40)])
+                                   (3, 96, 12288), (16, 64, 12288), (2, 4000, 40),
+                                   (8, 152001, 64)])          # (a vocabulary: tiles of 256 weight rows)
 @pytest.mark.parametrize("with_norm", [False, True])
 def test_few_row_product_plain(m, n, k, with_norm):
     """x . W^T for at most 16 rows, alone and with the residual add + norm as its prologue, in both output dtypes,
