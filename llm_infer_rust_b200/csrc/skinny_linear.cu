@@ -100,8 +100,9 @@ __device__ __forceinline__ float norm_weight(const void* w, int f32, int i) {
   return f32 ? static_cast<const float*>(w)[i] : __bfloat162float(static_cast<const bf16*>(w)[i]);
 }
 
-// MT: 64-row units of the weight tile (BN = 64 MT rows; a warp owns 16 MT of them).
-template <int MT>
+// MT: 64-row units of the weight tile (BN = 64 MT rows; a warp owns 16 MT of them).  EARLY_W: the norm's weights
+// of a warp's first pass over a row are fetched ahead of the dependency wait (see `launch` for when).
+template <int MT, bool EARLY_W>
 __global__ void __launch_bounds__(THREADS, 1)
 skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParams p) {
   constexpr int BN = 64 * MT;
@@ -180,8 +181,8 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   // The norm's weights for the columns that this lane takes in the first pass over a row (the only pass up to 1,024
   // columns): the same for every row and not written by the kernels before, so they are fetched ahead of the wait.
   // Widened to 32-bit here: kept packed, the loads were found to be scheduled after the wait.
-  float first_w[4][8];
-  if (p.residual != nullptr) {
+  float first_w[EARLY_W ? 4 : 1][8];
+  if (EARLY_W && p.residual != nullptr) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int k = (u * 32 + lane) * 8;
@@ -239,7 +240,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
             __align__(16) bf16 weighted[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              weighted[i] = __float2bfloat16_rn(k >= K ? 0.0f : sum[i] * (k0 == 0 ? first_w[u][i] : norm_weight(p.norm_w, p.norm_w_f32, k + i)));
+              weighted[i] = __float2bfloat16_rn(k >= K ? 0.0f : sum[i] * (EARLY_W && k0 == 0 ? first_w[EARLY_W ? u : 0][i] : norm_weight(p.norm_w, p.norm_w_f32, k + i)));
             *reinterpret_cast<uint4*>(xs + m * ldx + (k - k_lo)) = *reinterpret_cast<uint4*>(weighted);
           }
         }
@@ -483,20 +484,31 @@ static int choose_ksplit(int m, int n_tiles, int k, int sm_count) {
   return split < 1 ? 1 : split;
 }
 
-template <int MT>
-static int launch(const CUtensorMap& map, const SkinnyParams& p, int n_tiles, cudaStream_t stream) {
+template <int MT, bool EARLY_W>
+static int launch_as(const CUtensorMap& map, const SkinnyParams& p, int n_tiles, cudaStream_t stream) {
   constexpr int BN = 64 * MT;
   constexpr int STAGES = W_RING_BYTES / (BN * 128);
   const size_t smem = 1024 + W_RING_BYTES + XS_BYTES + MMAX * (BN + 1) * sizeof(float) + 2 * STAGES * sizeof(uint64_t) +
                       MMAX * sizeof(float) + 64;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(skinny_linear_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(skinny_linear_kernel<MT, EARLY_W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return b200_launch(skinny_linear_kernel<MT>, dim3(n_tiles * p.ksplit), dim3(THREADS), smem, stream, p.ksplit, map, p);
+  return b200_launch(skinny_linear_kernel<MT, EARLY_W>, dim3(n_tiles * p.ksplit), dim3(THREADS), smem, stream, p.ksplit,
+                     map, p);
+}
+
+// Which of the two compiled variants runs is a matter of measurement (decode steps at batch 8, both variants for
+// every product): rows under 4,096 columns are faster with the early fetch compiled in, also the products that have
+// no norm and skip it (1.735 against 1.79 ms a step at the 0.6B sizes); from 4,096 columns on the variant without
+// it wins (5.01 against 5.17 ms at the 8B sizes), where a warp passes over a row four times or more.
+template <int MT>
+static int launch(const CUtensorMap& map, const SkinnyParams& p, int n_tiles, cudaStream_t stream) {
+  if (p.K < 4096) return launch_as<MT, true>(map, p, n_tiles, stream);
+  return launch_as<MT, false>(map, p, n_tiles, stream);
 }
 
 // `params`: a SkinnyParams filled by the caller (ksplit is chosen here); `w_map`: the descriptor of the weight.
