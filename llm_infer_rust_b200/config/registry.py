@@ -40,11 +40,13 @@ def resolve_architecture(raw_config: dict) -> Architecture:
         raise ConfigError("config must be an object")
     names = raw_config.get("architectures")
     model_type = raw_config.get("model_type")
-    if not isinstance(names, list) or not names or not isinstance(model_type, str):
-        raise ConfigError("config.json needs model_type and a non-empty architectures list")
+    if not isinstance(names, list) or not names or not (model_type is None or isinstance(model_type, str)):
+        raise ConfigError("config.json needs a non-empty architectures list (and model_type, a string)")
+    # The architecture's name selects; a model_type that is given must agree with it (the reference
+    # wants both keys; a folder written without model_type is still named unambiguously).
     for name in names:
         arch = _ARCHITECTURES.get(name)
-        if arch is not None and arch.model_type == model_type:
+        if arch is not None and (model_type is None or arch.model_type == model_type):
             return arch
     raise ConfigError(f"unsupported model: model_type={model_type!r}, architectures={names!r}; "
                       f"registered: {registered_architectures()}")

@@ -127,7 +127,10 @@ def test_registry_resolves_and_refuses():
         r.update(model_type=model_type, architectures=names)
         with pytest.raises(ConfigError, match="unsupported model"):
             resolve_architecture(r)
-    for broken in ({}, {"model_type": "qwen3"}, {"model_type": "qwen3", "architectures": []}, []):
+    by_name = raw()
+    del by_name["model_type"]
+    assert resolve_architecture(by_name).name == "Qwen3ForCausalLM"
+    for broken in ({}, {"model_type": "qwen3"}, {"model_type": 3, "architectures": ["Qwen3ForCausalLM"]}, {"model_type": "qwen3", "architectures": []}, []):
         with pytest.raises(ConfigError):
             resolve_architecture(broken)
 
