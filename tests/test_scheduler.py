@@ -266,3 +266,110 @@ def test_a_request_that_ends_while_its_successor_step_runs_is_a_dead_row():
     with pytest.raises(ValueError):
         s.commit_step(nxt, [20, 21])                         # still one token for every sampling row
     assert cache.check() == ""
+
+
+# ---------------------------------------------------------------- random traffic
+@pytest.mark.parametrize("seed", range(16))
+def test_random_traffic_keeps_every_promise(seed):
+    """Requests arrive, are aborted and draw stop ids at random; steps are planned ahead wherever the scheduler
+    allows it.  Whatever the order: a plan never exceeds the budget of prompt tokens or the number of rows, every
+    decoding request is in every plan, a running request always gets its pages, requests start in arrival order,
+    each ends once with a reason that fits, and in the end no page, promise or slot is left behind."""
+    import random
+    rng = random.Random(seed)
+    page_size = rng.choice([1, 2, 4, 16])
+    max_seq = rng.randrange(8, 48)
+    pages = rng.randrange(-(-max_seq // page_size), 4 * -(-max_seq // page_size) + 2)
+    max_running = rng.randrange(1, 6)
+    budget = rng.choice([0, 3, 5, 16])
+    window = rng.choice([0, 0, 6])
+    stop = 7
+    cache, s = make(pages=pages, page_size=page_size, max_running=max_running, max_seq=max_seq, budget=budget,
+                    eos=[stop], window=window)
+    wanted = {}                                  # uid -> (prompt length, max_tokens, ignore_eos)
+    tokens, reasons, first_seen = {}, {}, []
+    to_come = rng.randrange(5, 30)
+
+    def note(out):
+        for o in out:
+            assert o.uid in wanted and o.uid not in reasons, "a request reported after it had ended"
+            if o.token >= 0:
+                tokens.setdefault(o.uid, []).append(o.token)
+            else:
+                assert o.finished and o.reason in (rt.FinishReason.Abort, rt.FinishReason.Error)
+            if o.finished:
+                reasons[o.uid] = o.reason
+
+    def check_plan(plan, ahead):
+        uids = [e.uid for e in plan.entries]
+        assert len(set(uids)) == len(uids) and len(uids) <= max_running
+        prompt_tokens = sum(e.count for e in plan.entries if e.start < wanted[e.uid][0])
+        if not ahead:
+            assert prompt_tokens == plan.prefill_tokens
+            assert budget == 0 or prompt_tokens <= budget
+            for uid in wanted:
+                if s.status_of(uid) == rt.Status.Decoding:
+                    assert uid in uids, "a decoding request was left out of a step"
+        for e in plan.entries:
+            if e.uid not in first_seen:
+                first_seen.append(e.uid)
+            assert cache.length(e.uid) == e.start
+            assert cache.grow(e.uid, e.start + e.count), "a running request ran out of pages"
+            cache.advance(e.uid, e.start + e.count)
+            assert e.start + e.count <= max_seq
+
+    def draw(plan):
+        return [stop if rng.random() < 0.08 else rng.randrange(8, 100) for e in plan.entries if e.sample]
+
+    flight = None                                # a step that was planned ahead and is "on the GPU"
+    steps = 0
+    while to_come or not s.is_idle() or flight is not None:
+        steps += 1
+        assert steps < 5000, "the scheduler makes no progress"
+        for _ in range(min(rng.choice([0, 0, 1, 2]), to_come)):
+            to_come -= 1
+            n, m, ig = rng.randrange(0, max_seq + 3), rng.randrange(1, 12), rng.random() < 0.5
+            uid = s.add_request([rng.randrange(8, 100) for _ in range(n)], params(max_tokens=m, ignore_eos=ig))
+            wanted[uid] = (n, m, ig)
+        if wanted and rng.random() < 0.1:
+            victim = rng.choice(sorted(wanted))
+            alive = s.status_of(victim) != rt.Status.Finished
+            assert s.abort_request(victim) == alive
+        note(s.drain_outbox())
+        if flight is None:
+            plan = s.plan_step()
+            note(s.drain_outbox())
+            if not plan.entries:
+                assert cache.check() == ""
+                continue
+            check_plan(plan, ahead=False)
+        else:
+            plan, flight = flight, None
+        following = s.successor(plan)
+        if following.entries and rng.random() < 0.8:
+            assert [e.uid for e in following.entries] == [e.uid for e in plan.entries]
+            check_plan(following, ahead=True)
+            flight = following
+        if rng.random() < 0.03:
+            note(s.fail_step(plan))
+            if flight is not None:               # the engine drops the step that it launched ahead with it
+                flight = None
+        else:
+            note(s.commit_step(plan, draw(plan)))
+        assert cache.check() == ""
+
+    assert cache.live_requests() == 0 and cache.free_state_slots() == max_running
+    for g in range(cache.num_groups()):
+        assert cache.free_pages(g) == pages and cache.unpromised_pages(g) == pages
+    assert set(reasons) == set(wanted), "every request ends, once"
+    assert first_seen == sorted(first_seen), "requests start in the order of their arrival"
+    for uid, (n, m, ignore) in wanted.items():
+        got, why = tokens.get(uid, []), reasons[uid]
+        assert len(got) <= m and n + max(len(got) - 1, 0) <= max(max_seq, n)   # the last token is never cached
+        if n == 0 or n > max_seq:
+            assert why == rt.FinishReason.Abort and not got
+        if why == rt.FinishReason.Stop:
+            assert got[-1] == stop and not ignore and stop not in got[:-1]
+        elif why == rt.FinishReason.Length:
+            assert len(got) == m or n + len(got) >= max_seq
+            assert ignore or stop not in got
