@@ -123,3 +123,70 @@ def test_refusals():
         build(m, [(1, [1, 2], [2])])
     with pytest.raises(Exception, match="no page"):
         build(m, [(1, [1, 2, 3], [])])          # pages cover two tokens only
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_steps_against_a_recount(seed):
+    """Random requests, portions and groups (one keeps all keys, one a window; pages of different sizes): every
+    array of every step is counted again here from the requests' lengths and block tables."""
+    import random
+    rng = random.Random(seed)
+    specs = [rt.GroupSpec(rng.choice([1, 2, 4, 16]), 200, 0)]
+    if rng.random() < 0.6:
+        specs.append(rt.GroupSpec(rng.choice([1, 2, 4, 8]), 200, rng.randrange(3, 20)))
+    m = rt.CacheManager(specs, 6)
+    live, next_id = [], 1
+    for _ in range(60):
+        while len(live) < 4 and (not live or rng.random() < 0.5):
+            m.open(next_id)
+            live.append(next_id)
+            next_id += 1
+        rows = []
+        for rid in rng.sample(live, rng.randrange(1, len(live) + 1)):
+            n = rng.choice([1, 1, 2, 3, 5, 9])
+            want = [rng.randrange(n) for _ in range(rng.choice([0, 1, 1, n]))]
+            rows.append((rid, [rng.randrange(1000) for _ in range(n)], want))
+            assert m.grow(rid, m.length(rid) + n)
+        pad = rng.choice([0, 0, len(rows) + 2]) if all(len(r[1]) == 1 for r in rows) else 0
+        widest = max(m.length(r[0]) + len(r[1]) for r in rows)
+        fixed = [-(-(widest + 7) // s.page_size) for s in specs] if pad else None
+        lay, a = build(m, rows, pad_to=pad, fixed=fixed)
+        R = max(len(rows), pad)
+        counts = [len(r[1]) for r in rows] + [1] * (R - len(rows))
+        prefix = [m.length(r[0]) for r in rows] + [0] * (R - len(rows))
+        cu = [0]
+        for c in counts:
+            cu.append(cu[-1] + c)
+        assert (lay.num_rows, lay.num_real_rows, lay.num_tokens) == (R, len(rows), cu[-1])
+        assert a["tokens"] == [t for r in rows for t in r[1]] + [0] * (R - len(rows))
+        assert a["positions"] == [p + i for p, c in zip(prefix, counts) for i in range(c)]
+        assert a["row_of_token"] == [r for r, c in enumerate(counts) for _ in range(c)]
+        assert a["cu_q"] == cu and a["prefix_len"] == prefix and a["kv_len"] == [p + c for p, c in zip(prefix, counts)]
+        assert a["state_slot"] == [m.state_slot(r[0]) for r in rows] + [0] * (R - len(rows))
+        assert a["decode_rows"] == [r for r, c in enumerate(counts) if c == 1]
+        assert a["prefill_rows"] == [r for r, c in enumerate(counts) if c > 1]
+        assert a["logit_rows"] == [cu[r] + i for r, row in enumerate(rows) for i in row[2]] + cu[len(rows):R]
+        assert lay.max_q_len == max(counts) and lay.max_kv_len == max(p + c for p, c in zip(prefix, counts))
+        for g, spec in enumerate(specs):
+            P = spec.page_size
+            width = fixed[g] if fixed else -(-lay.max_kv_len // P)
+            assert lay.table_width[g] == width
+            slots, table = [], []
+            for r, row in enumerate(rows):
+                held = list(m.block_table(row[0], g))
+                used = -(-(prefix[r] + counts[r]) // P)
+                assert all(page == 0 for page in held[:m.first_live_page(row[0], g)])
+                assert all(page > 0 for page in held[m.first_live_page(row[0], g):used])
+                table.append((held[:used] + [0] * width)[:width])
+                slots += [held[(prefix[r] + i) // P] * P + (prefix[r] + i) % P for i in range(counts[r])]
+            assert a["slots"][g] == slots + [0] * (R - len(rows))
+            assert a["tables"][g] == table + [[0] * width] * (R - len(rows))
+        for rid, tokens, _ in rows:
+            m.advance(rid, m.length(rid) + len(tokens))
+        assert m.check() == ""
+        for rid in [r for r in live if rng.random() < 0.08 or m.length(r) > 150]:
+            assert m.release(rid)
+            live.remove(rid)
+    for rid in live:
+        m.release(rid)
+    assert m.check() == "" and all(m.free_pages(g) == 200 for g in range(len(specs)))
