@@ -38,7 +38,17 @@ class SafetensorsFile:
 
     def __init__(self, path: str):
         self.path = path
+        self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
         self._fh = open(path, "rb")
+        try:
+            self._read_header()
+            self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
+        except Exception:
+            self._fh.close()
+            raise
+
+    def _read_header(self) -> None:
+        path = self.path
         size = os.fstat(self._fh.fileno()).st_size
         if size < 8:
             raise SafetensorsError(f"{path}: too short for a safetensors header")
@@ -49,16 +59,20 @@ class SafetensorsFile:
             header = json.loads(self._fh.read(header_len))
         except ValueError as err:
             raise SafetensorsError(f"{path}: header is not JSON: {err}") from None
+        if not isinstance(header, dict):
+            raise SafetensorsError(f"{path}: header is not a JSON object")
         header.pop("__metadata__", None)
         self._data_start = 8 + header_len
-        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
-        self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
         for name, info in header.items():
-            if info["dtype"] not in _DTYPES:
-                raise SafetensorsError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
-            begin, end = info["data_offsets"]
-            dtype = _DTYPES[info["dtype"]]
-            shape = tuple(int(s) for s in info["shape"])
+            try:
+                code, shape, (begin, end) = info["dtype"], tuple(info["shape"]), info["data_offsets"]
+                if any(isinstance(v, bool) or not isinstance(v, int) or v < 0 for v in shape + (begin, end)):
+                    raise ValueError("sizes and offsets must be non-negative integers")
+            except (KeyError, TypeError, ValueError) as err:
+                raise SafetensorsError(f"{path}: tensor {name} has a malformed header entry: {err!r}") from None
+            if code not in _DTYPES:
+                raise SafetensorsError(f"{path}: tensor {name} has unsupported dtype {code}")
+            dtype = _DTYPES[code]
             count = 1
             for s in shape:
                 count *= s

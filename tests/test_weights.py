@@ -162,3 +162,35 @@ def test_a_truncated_file_is_refused(tmp_path):
     path.write_bytes(data[: len(data) // 2])
     with pytest.raises(SafetensorsError, match="inconsistent offsets"):
         Checkpoint(str(tmp_path))
+
+
+def test_malformed_headers_are_refused_with_the_container_error(tmp_path):
+    import struct
+    path = tmp_path / "model.safetensors"
+
+    def stored(header, data=b"\0" * 16):
+        text = header if isinstance(header, bytes) else json.dumps(header).encode()
+        path.write_bytes(struct.pack("<Q", len(text)) + text + data)
+
+    good = {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 16]}}
+    stored(good)
+    assert Checkpoint(str(tmp_path)).read("a").shape == (2, 2)
+    for header, what in (
+            (b"{not json", "not JSON"), ([1, 2], "not a JSON object"),
+            ({"a": {"dtype": "F32", "shape": [2, 2]}}, "malformed"),
+            ({"a": [1, 2, 3]}, "malformed"),
+            ({"a": {"dtype": "F32", "shape": [2, "2"], "data_offsets": [0, 16]}}, "malformed"),
+            ({"a": {"dtype": "F32", "shape": [-2, -2], "data_offsets": [0, 16]}}, "malformed"),
+            ({"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0]}}, "malformed"),
+            ({"a": {"dtype": "F8_E4M3", "shape": [16], "data_offsets": [0, 16]}}, "unsupported dtype"),
+            ({"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [4, 16]}}, "inconsistent offsets"),
+            ({"a": {"dtype": "F32", "shape": [2, 4], "data_offsets": [0, 32]}}, "inconsistent offsets")):
+        stored(header)
+        with pytest.raises(SafetensorsError, match=what):
+            Checkpoint(str(tmp_path))
+    path.write_bytes(struct.pack("<Q", 1 << 40) + b"{}")
+    with pytest.raises(SafetensorsError, match="exceeds the file"):
+        Checkpoint(str(tmp_path))
+    path.write_bytes(b"abc")
+    with pytest.raises(SafetensorsError, match="too short"):
+        Checkpoint(str(tmp_path))
