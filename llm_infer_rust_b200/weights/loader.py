@@ -19,7 +19,7 @@ from typing import Dict, List, Sequence
 import torch
 
 from .plan import WeightBinding
-from .safetensors_io import Checkpoint, SafetensorsError
+from .safetensors_io import Checkpoint
 
 
 class WeightError(RuntimeError):
@@ -86,10 +86,7 @@ def load_weights(model, plan: Sequence[WeightBinding], model_dir: str,
     ``model`` needs ``bind_parameter(path, tensor)`` and ``parameter(path)``.
     Returns the checkpoint tensor names that were loaded.
     """
-    try:
-        ckpt = Checkpoint(model_dir)
-    except SafetensorsError:
-        raise
+    ckpt = Checkpoint(model_dir)
     loaded: List[str] = []
     try:
         check_checkpoint(ckpt, plan, model_dir)
