@@ -31,6 +31,11 @@ Options (as in the reference where it has them):
   --dtype NAME              Model dtype: auto, bfloat16, float32
   --device NAME             Device: auto or cuda (default auto)
   --log-level LEVEL         trace/debug/info/warn/error (default info)
+  --tp-size N               Tensor parallel size (only 1 is supported)
+Accepted from the reference's command line and without effect here (there is no HTTP server, one attention
+backend, one way of uploading a step's index arrays):
+  --host IP  --port PORT  --log-dir PATH  --trust-remote-code  --attention-backend fa|pt|flashinfer
+  --enable-consecutive-prefill-overlap  --disable-async-metadata
 Prompts and sampling (token ids in, token ids out):
   --prompt-ids IDS          Comma-separated token ids; may be given several times (else JSON lists on stdin)
   --temperature T  --top-k K  --top-p P  --max-tokens N  --ignore-eos  --seed S
@@ -40,6 +45,21 @@ Random-weights mode (writes the model folder, then serves it if prompts are give
   --seed S                  Seed of the random weights (and of sampling)
   --init-std X  --norm-std X   N(0, X) matrices (default 0.02); norm weights 1 + N(0, X) (default 0)
   -h, --help                Show this help"""
+
+
+# Options of the reference's server (src/server/cli.rs:13-36) that a launch script may carry over: they are read
+# and have no effect.
+WITHOUT_EFFECT_VALUED = {"--host": None, "--port": None, "--log-dir": None,
+                         "--attention-backend": ["fa", "pt", "flashinfer"]}
+WITHOUT_EFFECT_SWITCHES = ("--trust-remote-code", "--enable-consecutive-prefill-overlap", "--disable-async-metadata")
+
+
+def given_without_effect(args: argparse.Namespace) -> List[str]:
+    """The options of the reference's server that were given and do nothing here."""
+    def dest(flag):
+        return flag.lstrip("-").replace("-", "_")
+    return [f for f in WITHOUT_EFFECT_VALUED if getattr(args, dest(f)) is not None] + \
+           [f for f in WITHOUT_EFFECT_SWITCHES if getattr(args, dest(f))]
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -58,7 +78,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--dtype", default="auto", choices=["auto", "bfloat16", "float32"])
     p.add_argument("--device", default="auto", choices=["auto", "cuda"])
-    p.add_argument("--log-level", default="info", choices=["trace", "debug", "info", "warn", "error"])
+    p.add_argument("--log-level", default="info", type=lambda v: "warn" if v.lower() == "warning" else v.lower(),
+                   choices=["trace", "debug", "info", "warn", "error"])
+    p.add_argument("--tp-size", type=int, default=1)
+    for flag in WITHOUT_EFFECT_VALUED:
+        p.add_argument(flag, default=None, choices=WITHOUT_EFFECT_VALUED[flag])
+    for flag in WITHOUT_EFFECT_SWITCHES:
+        p.add_argument(flag, action="store_true")
     p.add_argument("--prompt-ids", action="append", default=[])
     p.add_argument("--temperature", type=float, default=0.0)
     p.add_argument("--top-k", type=int, default=-1)
@@ -95,6 +121,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     if not args.model_path:
         print("--model-path is required\n" + USAGE, file=sys.stderr)
         return 2
+    if args.tp_size != 1:
+        print("--tp-size: only 1 is supported (this engine runs on one GPU)", file=sys.stderr)
+        return 2
+    ignored = given_without_effect(args)
+    if ignored and args.log_level in ("trace", "debug", "info"):
+        print("note: " + ", ".join(ignored) + " accepted, without effect here", file=sys.stderr)
     if args.random_weights:
         if not args.config:
             print("--random-weights needs --config PATH", file=sys.stderr)

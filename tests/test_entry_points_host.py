@@ -34,7 +34,15 @@ def test_option_names_and_defaults_are_the_references():
     assert (a.max_total_tokens, a.max_prefill_tokens_per_batch, a.chunked_prefill_size, a.cuda_graph_bs) == (640, 0, -1, 0)
     assert a.disable_cpu_gpu_overlap and a.ignore_eos and a.seed == 3
     assert cli.read_prompts(a) == [[1, 2, 3], [4]]
-    for refused in (["--dtype", "float16"], ["--device", "cpu"], ["--log-level", "loud"]):
+    # the reference's server options that a launch script may carry over are read and do nothing
+    a = cli.parse_args(["--model-path", "m", "--host", "0.0.0.0", "--port", "9001", "--tp-size", "1", "--log-dir", "l",
+                        "--attention-backend", "flashinfer", "--trust-remote-code", "--disable-async-metadata",
+                        "--enable-consecutive-prefill-overlap", "--log-level", "WARNING"])
+    assert a.log_level == "warn" and a.tp_size == 1
+    assert cli.given_without_effect(a) == ["--host", "--port", "--log-dir", "--attention-backend", "--trust-remote-code",
+                                           "--enable-consecutive-prefill-overlap", "--disable-async-metadata"]
+    assert cli.given_without_effect(cli.parse_args(["--model-path", "m"])) == []
+    for refused in (["--dtype", "float16"], ["--device", "cpu"], ["--log-level", "loud"], ["--attention-backend", "x"]):
         with pytest.raises(SystemExit):
             cli.parse_args(["--model-path", "m"] + refused)
 
@@ -43,6 +51,7 @@ def test_the_command_line_without_a_model_or_prompts(tmp_path, capsys):
     assert cli.main(["--help"]) == 0 and "--max-running-req" in capsys.readouterr().out
     assert cli.main([]) == 2 and "--model-path is required" in capsys.readouterr().err
     assert cli.main(["--model-path", str(tmp_path), "--random-weights"]) == 2
+    assert cli.main(["--model-path", str(tmp_path), "--tp-size", "2"]) == 2 and "only 1" in capsys.readouterr().err
     # random-weights mode writes a model folder and, with no prompts, stops there (no GPU is asked for)
     raw = {"model_type": "qwen3", "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 1, "hidden_size": 32,
            "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 48,
