@@ -39,11 +39,25 @@ class WeightError(RuntimeError):
 
 
 def read_config_json(model_dir: str) -> dict:
+    """config.json of a model folder.  If the folder also has a generation_config.json with an ``eos_token_id``,
+    that one replaces config.json's (the reference's order: src/server/components/generation.rs:7-44)."""
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):
         raise FileNotFoundError(f"{model_dir}: no config.json")
     with open(path) as fh:
-        return json.load(fh)
+        config = json.load(fh)
+    generation_path = os.path.join(model_dir, "generation_config.json")
+    if isinstance(config, dict) and os.path.isfile(generation_path):
+        with open(generation_path) as fh:
+            try:
+                generation = json.load(fh)
+            except ValueError as err:
+                raise ValueError(f"{generation_path}: not JSON: {err}") from None
+        if not isinstance(generation, dict):
+            raise ValueError(f"{generation_path}: generation config must be an object")
+        if "eos_token_id" in generation:
+            config["eos_token_id"] = generation["eos_token_id"]
+    return config
 
 
 def kept_dtype(stored: torch.dtype, engine_dtype: torch.dtype) -> torch.dtype:

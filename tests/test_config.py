@@ -156,3 +156,26 @@ def test_run_list_is_validated():
         with pytest.raises(ConfigError):
             dataclasses.replace(spec, run_list=bad).validate()
     dataclasses.replace(spec, run_list=(RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, reads=1))).validate()
+
+
+def test_generation_config_names_the_stop_ids_first(tmp_path):
+    # src/server/components/generation.rs:7-44: generation_config.json's eos_token_id, else config.json's
+    import json
+    from llm_infer_rust_b200.weights.loader import read_config_json
+    r = raw()
+    r["eos_token_id"] = 3
+    (tmp_path / "config.json").write_text(json.dumps(r))
+    assert Qwen3Config.parse(read_config_json(str(tmp_path))).eos_token_ids == (3,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.6}))
+    assert Qwen3Config.parse(read_config_json(str(tmp_path))).eos_token_ids == (3,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [5, 4]}))
+    assert Qwen3Config.parse(read_config_json(str(tmp_path))).eos_token_ids == (5, 4)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": None}))
+    assert Qwen3Config.parse(read_config_json(str(tmp_path))).eos_token_ids == ()
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": r["vocab_size"]}))
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        Qwen3Config.parse(read_config_json(str(tmp_path)))
+    for broken in ("[1, 2]", "{not json"):
+        (tmp_path / "generation_config.json").write_text(broken)
+        with pytest.raises(ValueError, match="generation_config.json"):
+            read_config_json(str(tmp_path))
