@@ -39,6 +39,13 @@ def _code(t: torch.Tensor) -> int:
 
 
 def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    """Checks that the operands are on the device.  Every wrapper that launches calls this first, so it is also
+    where products that wait in the chain (see ``chain_linear``) are launched: whatever runs next may read them."""
+    flush_chain()
+    _cuda_only(*tensors)
+
+
+def _cuda_only(*tensors: Optional[torch.Tensor]) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise KernelError("the kernels run on CUDA tensors only; there is no CPU path")
@@ -94,10 +101,12 @@ def error_word(device: torch.device) -> torch.Tensor:
 
 def check_errors(device: torch.device) -> None:
     """Read the error word (synchronises) and raise if a kernel flagged a fault."""
+    flush_chain()
     word = error_word(device)
     value = int(word.item())
     if value:
         word.zero_()
+        _reset_chain_state(device)
         what = [text for bit, text in ERROR_BITS.items() if value & bit]
         raise KernelError("a kernel refused an access: " + "; ".join(what))
 
@@ -117,6 +126,7 @@ class PendingRead:
         value = int(self.buf[self.n])
         if value:
             error_word(self.device).zero_()
+            _reset_chain_state(self.device)
             what = [text for bit, text in ERROR_BITS.items() if value & bit]
             raise KernelError("a kernel refused an access: " + "; ".join(what))
         return self.buf[:self.n].tolist()
@@ -126,6 +136,7 @@ def begin_read(ids: torch.Tensor) -> PendingRead:
     """Start copying ``ids`` (int32, on the device) and the error word into pinned memory (two small copies on
     the current stream, then an event).  Four staging buffers per device take turns: at most three reads may be
     pending when a fourth begins."""
+    flush_chain()
     device = ids.device
     key = device.index or 0
     n = ids.numel()
@@ -412,21 +423,26 @@ class _SkinnyParams(ctypes.Structure):
 
 
 class PendingNorm:
-    """A residual add + RMSNorm that has not run: the product that consumes it runs it as its prologue.
+    """An RMSNorm (with or without a residual add before it) that has not run: the product that consumes it runs
+    it as its prologue.
 
-    ``residual_out`` is the tensor that will hold the rounded sum (None: the sum is not kept).
-    ``materialize()`` runs the norm as a kernel of its own, for a consumer that cannot fuse it.
+    ``residual`` None: the plain norm of ``x``.  ``residual_out`` is the tensor that will hold the rounded sum
+    (None: the sum is not kept).  ``materialize()`` runs the norm as a kernel of its own, for a consumer that
+    cannot fuse it.
     """
 
     def __init__(self, x, residual, weight, eps, rows=None, write_residual=True):
         self.x, self.residual, self.weight, self.eps, self.rows = x, residual, weight, float(eps), rows
-        self.residual_out = torch.empty_like(residual) if write_residual else None
+        self.residual_out = torch.empty_like(residual) if write_residual and residual is not None else None
         self.dtype, self.device = x.dtype, x.device
         n = x.shape[0] if rows is None else rows.numel()
         self.shape = (n, x.shape[-1])
 
     def materialize(self) -> torch.Tensor:
+        if self.residual is None:
+            return rms_norm(self.x, self.weight, self.eps, rows=self.rows)
         if self.residual_out is not None:
+            flush_chain()
             self.residual_out.copy_(self.residual)
             return add_rms_norm(self.x, self.residual_out, self.weight, self.eps, rows=self.rows)
         return add_rms_norm(self.x, self.residual, self.weight, self.eps, rows=self.rows, write_residual=False)
@@ -482,20 +498,7 @@ def skinny_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int
         return False
     if mode == EPI_SWIGLU and weight.shape[0] % 2:
         return False
-    if mode != EPI_QKV and 2 * weight.shape[0] * k < TUNE_FROM_BYTES:
-        # One CTA per 128 weight rows (64 gate + 64 up): when they make more than one wave of the SMs and the
-        # last wave is badly filled (192 tiles on 148 SMs run as long as 296), the library product is faster.
-        # (Larger weights are routed by measurement: few_row_pays.)
-        sms = _sm_count(weight.device)
-        tiles = -(-weight.shape[0] // 128)
-        if tiles > sms and tiles / (sms * -(-tiles // sms)) < 0.8:
-            return False
     return True
-
-
-_tuned = {}
-_flush_buffers = {}
-TUNE_FROM_BYTES = 24 << 20              # weights from this size on are routed by measurement
 
 
 @contextlib.contextmanager
@@ -506,106 +509,17 @@ def graph_capture(graph: "torch.cuda.CUDAGraph"):
     owns CUDA graphs or device memory (an engine that the caller dropped, say) is else freed at whatever allocation
     inside the capture happens to start a collection; destroying a graph or returning its memory is not permitted
     while a stream captures, and the capture ends with "operation failed due to a previous error during capture"."""
+    flush_chain()
     gc.collect()
     held = gc.isenabled()
     gc.disable()
     try:
         with torch.cuda.graph(graph):
             yield
+            flush_chain()
     finally:
         if held:
             gc.enable()
-
-
-def _timed_cold(fn, device) -> float:
-    """Median time in ms of ``fn()`` replayed as a CUDA graph (as it will run inside a step: the library chooses
-    other kernels under capture than in eager mode) with the L2 flushed before every run (weights come from HBM in
-    a real step)."""
-    key = torch.device(device).index or 0
-    flush = _flush_buffers.get(key)
-    if flush is None:
-        flush = _flush_buffers[key] = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-    fn()
-    fn()                                                      # loads the kernels, sets the library up
-    torch.cuda.synchronize(device)
-    graph = torch.cuda.CUDAGraph()
-    with graph_capture(graph):
-        fn()
-    times = []
-    for _ in range(6):
-        flush.zero_()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        graph.replay()
-        end.record()
-        end.synchronize()
-        times.append(start.elapsed_time(end))
-    del graph
-    return sorted(times[1:])[len(times) // 2 - 1]
-
-
-def few_row_pays(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
-                 head_dim: int = 0, fused_norm: bool = False) -> bool:
-    """Whether the few-row kernel (with the norm before it and the epilogue after it fused in) is the faster
-    way to this product than the library product with those as kernels of their own.
-
-    Small matrices (under TUNE_FROM_BYTES) and float32 results (the head) always take the kernel: there launches
-    decide and it has fewest.  For larger ones it is measured, once per process for every (weight shape, epilogue, norm or not, 1 / up to 8 / up
-    to 16 rows): the kernel wins where the library's choice for the shape is poor, the library on some large
-    matrices (each CTA of the kernel normalises the rows itself and keeps its K-slice of them in shared memory).  During a graph capture nothing is measured (a capture is
-    preceded by a run of the same step outside it, which has asked already)."""
-    if not skinny_ok(rows, weight, act_dtype, mode, head_dim):
-        return False
-    bucket = 1 if rows == 1 else (8 if rows <= 8 else SKINNY_MAX_ROWS)
-    key = (weight.device.index or 0, weight.shape[0], weight.shape[1], mode, bool(fused_norm), bucket)
-    known = _tuned.get(key)
-    if known is not None:
-        return known
-    n, k = weight.shape
-    # Not measured: small matrices; the head (once a step; given to the library, 64 us against 81 us for the product
-    # at the 0.6B shape, a prefill step of 255 kernels took 0.1 ms LONGER, all of it in gaps between other kernels:
-    # a measurement of one product does not see what another kind of node does to the rest of a step's graph, and
-    # only the layers' products of large models are worth that risk).
-    if torch.cuda.is_current_stream_capturing() or 2 * n * k < TUNE_FROM_BYTES or mode == EPI_PLAIN_F32:
-        return True
-    dev = weight.device
-    # the QKV epilogue needs a cache and positions: it is timed as the plain product, its library rival with
-    # one more small kernel (per-head norm, rotation, cache store), which at these row counts is launch time
-    kernel_mode = EPI_PLAIN_BF16 if mode == EPI_QKV else mode
-    if kernel_mode != mode and not skinny_ok(bucket, weight, act_dtype, kernel_mode):
-        _tuned[key] = True
-        return True
-    x = torch.randn(bucket, k, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    residual = torch.randn(bucket, k, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    norm_w = torch.ones(k, device=dev, dtype=torch.bfloat16)
-    scratch_res = residual.clone()
-
-    def fused():
-        skinny_linear(PendingNorm(x, residual, norm_w, 1e-6) if fused_norm else x, weight, kernel_mode)
-
-    def library():
-        y = x
-        if fused_norm:
-            y = add_rms_norm(x, scratch_res, norm_w, 1e-6)        # (the residual is updated in place, as in a step)
-        if mode == EPI_PLAIN_F32:
-            torch.mm(y, weight.t(), out_dtype=torch.float32)
-            return
-        z = torch.mm(y, weight.t())
-        if mode == EPI_SWIGLU or (mode == EPI_QKV and n % 2 == 0):
-            silu_mul(z)                                       # (QKV: stands in for the small kernel after the product)
-
-    before = launch_count()
-    t_fused, t_library = _timed_cold(fused, dev), _timed_cold(library, dev)
-    add_launches(before - launch_count())                     # measurements are not the model's launches
-    # Measured alone, the kernel is charged what it does not pay inside a step: launched with programmatic dependent
-    # launch it sets up, fetches its first weights and the epilogue's index data under the tail of the kernel before
-    # it (2 to 3 us a kernel in a decode step), and CUDA events resolve about 2 us.  The library must win by more.
-    _tuned[key] = t_fused <= t_library + 0.004
-    if os.environ.get("LLM_INFER_B200_LOG_ROUTING"):
-        print(f"[llm_infer_rust_b200] few-row product {n} x {k}, epilogue {mode}, norm {int(fused_norm)}, up to {bucket} "
-              f"rows: kernel {t_fused * 1e3:.1f} us, library {t_library * 1e3:.1f} us -> "
-              f"{'kernel' if _tuned[key] else 'library'}", file=sys.stderr, flush=True)
-    return _tuned[key]
 
 
 def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
@@ -618,6 +532,8 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     encoding and the cache store, with ``qkv`` = the keyword arguments of ``qkv_post`` (without ``qkv``);
     the result is then ``q_out``.
     """
+    if isinstance(x, PendingNorm) and x.residual is None:
+        x = x.materialize()                                    # (this kernel's prologue always adds a residual)
     pending = x if isinstance(x, PendingNorm) else None
     src = pending.x if pending is not None else x
     rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
@@ -681,6 +597,283 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     return out
 
 
+# --------------------------------------------------------------------------- chains of few-row products
+CHAIN_MAX_ROWS = 64
+PRO_NONE, PRO_ADD_NORM, PRO_NORM = 0, 1, 2
+# How products of few rows are routed: "single" (one kernel per product, up to 16 rows: csrc/skinny_linear.cu),
+# "chain" (one persistent kernel for consecutive products, up to 64 rows: csrc/linear_chain.cu) or "library" (cuBLAS
+# with the norm, rotation and activation as kernels of their own).  Fixed by the environment or by assignment,
+# never by a measurement, so that two processes given the same input run the same kernels.  Measured on B200
+# (decode, batch 8, context 4,096): "single" 1.73 ms a step at the Qwen3-0.6B sizes and 5.0 ms at the 8B sizes,
+# "chain" 1.86 ms and 6.2 ms (its barriers and tile hand-overs cost what the launches did), so "single" is the default.
+few_row_route = os.environ.get("LLM_INFER_B200_FEW_ROW", "single")
+single_max_bytes = int(os.environ.get("LLM_INFER_B200_SINGLE_MAX_BYTES", 224 << 20))
+# Weights up to this size are multiplied in tiles of 16 rows that one CTA owns (see csrc/linear_chain.cu).
+chain_narrow_bytes = int(os.environ.get("LLM_INFER_B200_CHAIN_NARROW_BYTES", 48 << 20))
+
+
+class _ChainOp(ctypes.Structure):
+    """Mirror of ``ChainOp`` in csrc/linear_chain.cu (same order, native alignment)."""
+    _fields_ = [("x", ctypes.c_void_p), ("x_rows", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+                ("residual_out", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("stats_in", ctypes.c_void_p),
+                ("stats_out", ctypes.c_void_p), ("stats_res_in", ctypes.c_void_p), ("stats_res_out", ctypes.c_void_p),
+                ("out", ctypes.c_void_p), ("q_w", ctypes.c_void_p), ("k_w", ctypes.c_void_p),
+                ("cos_table", ctypes.c_void_p), ("sin_table", ctypes.c_void_p), ("positions", ctypes.c_void_p),
+                ("slots", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("cache_slots", ctypes.c_longlong), ("prologue", ctypes.c_int), ("norm_w_f32", ctypes.c_int),
+                ("eps", ctypes.c_float), ("stats_tiles", ctypes.c_int), ("M", ctypes.c_int), ("N", ctypes.c_int),
+                ("K", ctypes.c_int), ("mode", ctypes.c_int), ("nh", ctypes.c_int), ("nkv", ctypes.c_int),
+                ("head_dim", ctypes.c_int), ("rot_dim", ctypes.c_int), ("max_pos", ctypes.c_int),
+                ("page_size", ctypes.c_int), ("qk_w_f32", ctypes.c_int), ("qk_eps", ctypes.c_float),
+                ("narrow", ctypes.c_int), ("box_rows", ctypes.c_int), ("tiles", ctypes.c_int), ("kblocks", ctypes.c_int), ("per", ctypes.c_int), ("ctas", ctypes.c_int),
+                ("first_cta", ctypes.c_int), ("ticket_off", ctypes.c_int)]
+
+
+def _chain_lib():
+    lib = load_cuda_library("linear_chain.cu")
+    if not getattr(lib, "_checked", False):
+        if lib.b200_chain_op_size() != ctypes.sizeof(_ChainOp):
+            raise KernelError("the product block of linear_chain.cu and its Python mirror differ")
+        lib.b200_chain_scratch_floats.restype = ctypes.c_longlong
+        lib._checked = True
+    return lib
+
+
+_chain_maps = {}
+_chain_state = {}
+_CHAIN_TICKETS = 1 << 16
+
+
+def _chain_map(weight: torch.Tensor, box_rows: int):
+    key = (weight.data_ptr(), tuple(weight.shape), box_rows)
+    buf = _chain_maps.get(key)
+    if buf is None:
+        buf = ctypes.create_string_buffer(128)
+        rc = _chain_lib().b200_chain_weight_map(buf, _p(weight), ctypes.c_longlong(weight.shape[0]),
+                                                ctypes.c_longlong(weight.shape[1]), box_rows)
+        if rc != 0:
+            raise KernelError(f"the TMA descriptor of a weight matrix could not be made (code {rc})")
+        if len(_chain_maps) > 8192:
+            _chain_maps.clear()
+        _chain_maps[key] = buf
+    return buf
+
+
+def _chain_buffers(device):
+    """Scratch for partial sums (sized for 64 rows on every SM: 9.7 MB), tickets and the grid barrier's words of
+    one device; made once, so that a graph may capture launches that use them."""
+    key = torch.device(device).index or 0
+    st = _chain_state.get(key)
+    if st is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the chain kernel's buffers must exist before a graph is captured")
+        floats = int(_chain_lib().b200_chain_scratch_floats(CHAIN_MAX_ROWS, _sm_count(device)))
+        st = _chain_state[key] = dict(scratch=torch.empty(floats, dtype=torch.float32, device=device),
+                                      tickets=torch.zeros(_CHAIN_TICKETS, dtype=torch.int32, device=device),
+                                      sync=torch.zeros(_chain_lib().b200_chain_sync_words(), dtype=torch.int32,
+                                                       device=device))
+    return st
+
+
+def _reset_chain_state(device) -> None:
+    """After a wait inside the chain kernel ran out its barrier words and tickets may hold anything."""
+    st = _chain_state.get(torch.device(device).index or 0)
+    if st is not None:
+        st["tickets"].zero_()
+        st["sync"].zero_()
+
+
+def chain_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
+                head_dim: int = 0) -> bool:
+    """Whether the chain kernel takes this product: bfloat16 activations and weight, at most 64 rows, K a multiple
+    of 8; QKV: a head size that divides 128."""
+    if act_dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.dim() != 2:
+        return False
+    if not 0 < rows <= CHAIN_MAX_ROWS or weight.shape[1] % 8 or not weight.is_contiguous() or weight.data_ptr() % 16:
+        return False
+    if mode == EPI_QKV and (head_dim <= 0 or 128 % head_dim):
+        return False
+    if mode == EPI_SWIGLU and weight.shape[0] % 2:
+        return False
+    return True
+
+
+def few_row_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
+                  head_dim: int = 0) -> bool:
+    """Whether a product of ``rows`` rows runs on this package's few-row kernels (with the norm before it and the
+    epilogue after it fused in) rather than as a library product with those as kernels of their own."""
+    if few_row_route == "chain" and chain_takes(rows, weight, act_dtype, mode, head_dim):
+        return True
+    if few_row_route == "library" or not skinny_ok(rows, weight, act_dtype, mode, head_dim):
+        return False
+    # The single-product kernel gives every CTA the rows of x to normalise and one tile of 128 weight rows; on the
+    # largest layer matrices (gate/up and down at the Qwen3-32B sizes, 262 and 524 MB) the library product with the norm
+    # and activation as kernels of their own was measured faster (14.8 against 18.9 ms a decode step at batch 8).
+    return mode == EPI_PLAIN_F32 or 2 * weight.shape[0] * weight.shape[1] < single_max_bytes
+
+
+class _Chain:
+    def __init__(self, device):
+        self.device = device
+        self.ops, self.weights, self.keep = [], [], []
+        self.by_out = {}                 # data pointer of a product's output -> (index, output tensor)
+        self.stats_from = {}             # index of a product -> index of the product that leaves its rows' statistics
+
+
+_chain: Optional[_Chain] = None
+# For tuning: an int64 tensor [SMs, 64] on the device; every CTA's first thread then leaves the nanosecond clock there at
+# eight places of every product of the next launches (start, barrier passed, row scales, x staged, products done,
+# sums added, epilogue done).
+chain_trace: Optional[torch.Tensor] = None
+chain_stages = int(os.environ.get("LLM_INFER_B200_CHAIN_STAGES", 8))
+
+
+def few_row_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
+                   qkv: Optional[dict] = None, lazy: bool = False) -> torch.Tensor:
+    """epilogue(prologue(x) . weight^T) for few rows; arguments as ``skinny_linear``.
+
+    ``lazy`` (on the "chain" route): the product is not launched here.  It joins the products that wait, and all
+    of them run in one persistent kernel when something else is about to be launched (``flush_chain``; every
+    wrapper of this module does that first).  The returned tensor is filled by then: code that touches it with
+    anything but this module's wrappers must call ``flush_chain()`` before.  Without ``lazy`` the product (and
+    whatever waited before it) is launched before this returns."""
+    pending = x if isinstance(x, PendingNorm) else None
+    src = pending.x if pending is not None else x
+    rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
+    m = src.shape[0] if rows_t is None else rows_t.numel()
+    head_dim = qkv["head_dim"] if qkv else 0
+    if few_row_route == "chain" and chain_takes(m, weight, src.dtype, mode, head_dim):
+        out = _chain_append(pending, src, rows_t, m, weight, mode, qkv)
+        if not lazy:
+            flush_chain()
+        return out
+    return skinny_linear(x, weight, mode, x_rows=x_rows, qkv=qkv)
+
+
+def _chain_append(pending, src, rows_t, m, weight, mode, qkv) -> torch.Tensor:
+    global _chain
+    _cuda_only(src, weight, rows_t)
+    _contig(src, weight, rows_t)
+    n, k = weight.shape
+    if src.shape[-1] != k or src.dim() != 2:
+        raise KernelError(f"the rows have {src.shape[-1]} columns, the weight has {k}")
+    dev = src.device
+    if _chain is not None and _chain.device != dev:
+        flush_chain()
+    if _chain is None:
+        _chain = _Chain(dev)
+    ch = _chain
+    op = _ChainOp()
+    op.x, op.x_rows = src.data_ptr(), (0 if rows_t is None else rows_t.data_ptr())
+    op.M, op.N, op.K, op.mode = m, n, k, mode
+    if pending is not None:
+        w = pending.weight
+        if w.numel() != k or w.dtype not in (torch.float32, torch.bfloat16) or not w.is_cuda:
+            raise KernelError("the norm weight must have K elements, bfloat16 or float32, on the device")
+        op.norm_w, op.norm_w_f32, op.eps = w.data_ptr(), int(w.dtype == torch.float32), pending.eps
+        op.prologue = PRO_NORM
+        if pending.residual is not None:
+            res = pending.residual
+            if res.dtype != torch.bfloat16 or res.shape != src.shape or not res.is_contiguous():
+                raise KernelError("the residual must be bfloat16, contiguous and have the shape of x")
+            op.prologue = PRO_ADD_NORM
+            op.residual = res.data_ptr()
+            made = ch.by_out.get(src.data_ptr())
+            if made is not None and made[1] is src and ch.ops[made[0]].mode == EPI_PLAIN_BF16 \
+                    and ch.ops[made[0]].stats_out is None:
+                # x is the output of a product of this chain: that product's epilogue adds the residual, stores the
+                # rounded sum and leaves the rows' sums of squares, so nobody has to read whole rows again
+                prev = ch.ops[made[0]]
+                tiles = _chain_lib().b200_chain_tiles(EPI_PLAIN_BF16, prev.N, 1)      # (narrow tiles are the most)
+                stats = torch.empty(tiles * CHAIN_MAX_ROWS, dtype=torch.float32, device=dev)
+                sum_out = pending.residual_out if pending.residual_out is not None else torch.empty_like(res)
+                prev.stats_out, prev.stats_res_in, prev.stats_res_out = stats.data_ptr(), res.data_ptr(), sum_out.data_ptr()
+                op.stats_in = stats.data_ptr()
+                ch.stats_from[len(ch.ops)] = made[0]          # (how many tiles wrote them is known at the launch)
+                ch.keep += [stats, sum_out]
+            else:
+                op.residual_out = 0 if pending.residual_out is None else pending.residual_out.data_ptr()
+        ch.keep.append(pending)
+    if mode == EPI_QKV:
+        nh, nkv, head_dim = qkv["num_heads"], qkv["num_kv_heads"], qkv["head_dim"]
+        out = qkv["q_out"]
+        kc, vc = qkv.get("k_cache"), qkv.get("v_cache")
+        qw, kw = qkv.get("q_weight"), qkv.get("k_weight")
+        cos, sin = qkv.get("cos"), qkv.get("sin")
+        slots = qkv.get("slots")
+        _cuda_only(out, kc, vc, qw, kw, cos, sin, qkv["positions"], slots)
+        _contig(out, kc, vc, qw, kw, cos, sin, qkv["positions"], slots)
+        if n != (nh + 2 * nkv) * head_dim or out.shape != (m, nh * head_dim) or out.dtype != torch.bfloat16:
+            raise KernelError("qkv sizes do not fit the weight")
+        if slots is not None and (kc is None or kc.dtype != torch.bfloat16 or kc.shape[1] != nkv or kc.shape[3] != head_dim
+                                  or vc is None or vc.dtype != torch.bfloat16):
+            raise KernelError("the cache must be bfloat16 [pages + 1, kv_heads, page_size, head_dim]")
+        if (qw is None) != (kw is None) or (qw is not None and qw.dtype != kw.dtype):
+            raise KernelError("q and k norm weights come together and share a dtype")
+        if cos is not None and (cos.dtype != torch.float32 or sin.dtype != torch.float32):
+            raise KernelError("rotary tables must be float32")
+        op.nh, op.nkv, op.head_dim, op.rot_dim = nh, nkv, head_dim, int(qkv.get("rot_dim", 0)) if cos is not None else 0
+        op.max_pos = 0 if cos is None else cos.shape[0]
+        op.page_size = 1 if kc is None else kc.shape[2]
+        op.cache_slots = 0 if kc is None else kc.shape[0] * kc.shape[2]
+        op.qk_eps = float(qkv.get("eps", 0.0))
+        op.q_w, op.k_w = (0 if qw is None else qw.data_ptr()), (0 if kw is None else kw.data_ptr())
+        op.qk_w_f32 = int(qw is not None and qw.dtype == torch.float32)
+        op.cos_table, op.sin_table = (0 if cos is None else cos.data_ptr()), (0 if sin is None else sin.data_ptr())
+        op.positions = qkv["positions"].data_ptr()
+        op.slots = 0 if slots is None else slots.data_ptr()
+        op.k_cache, op.v_cache = (0 if kc is None else kc.data_ptr()), (0 if vc is None else vc.data_ptr())
+        ch.keep.append(qkv)
+    elif mode == EPI_SWIGLU:
+        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=dev)
+    else:
+        out = torch.empty((m, n), dtype=torch.float32 if mode == EPI_PLAIN_F32 else torch.bfloat16, device=dev)
+    op.out = out.data_ptr()
+    ch.ops.append(op)
+    ch.weights.append(weight)
+    ch.keep += [src, rows_t, out]
+    ch.by_out[out.data_ptr()] = (len(ch.ops) - 1, out)
+    return out
+
+
+def chain_pending() -> int:
+    """Products that wait in the chain."""
+    return 0 if _chain is None else len(_chain.ops)
+
+
+def flush_chain() -> None:
+    """Launch the products that wait in the chain (at most six per launch of the persistent kernel)."""
+    global _chain
+    ch = _chain
+    if ch is None:
+        return
+    _chain = None
+    lib = _chain_lib()
+    st = _chain_buffers(ch.device)
+    most = lib.b200_chain_max_ops()
+    sms = _sm_count(ch.device)
+    groups = [range(at, min(at + most, len(ch.ops))) for at in range(0, len(ch.ops), most)]
+    for group in groups:                                   # the kind of tile depends on the launch's largest row count
+        rows = max(ch.ops[i].M for i in group)
+        for i in group:
+            op, w = ch.ops[i], ch.weights[i]
+            op.narrow = lib.b200_chain_narrow(op.mode, op.N, op.K, rows, ctypes.c_longlong(chain_narrow_bytes))
+            op.box_rows = lib.b200_chain_box_rows(op.mode, op.narrow)
+    for i, source in ch.stats_from.items():
+        ch.ops[i].stats_tiles = lib.b200_chain_tiles(ch.ops[source].mode, ch.ops[source].N, ch.ops[source].narrow)
+    with torch.cuda.device(ch.device):
+        for group in groups:
+            ops_now = [ch.ops[i] for i in group]
+            if sum(lib.b200_chain_tiles(o.mode, o.N, o.narrow) for o in ops_now) > _CHAIN_TICKETS:
+                raise KernelError("a chain of products has more tiles than the ticket array holds")
+            block = (_ChainOp * len(ops_now))(*ops_now)
+            maps = ctypes.create_string_buffer(b"".join(_chain_map(ch.weights[i], ch.ops[i].box_rows).raw for i in group),
+                                               128 * len(ops_now))
+            rc = lib.b200_linear_chain(block, maps, len(ops_now), _p(st["scratch"]), _p(st["tickets"]), _p(st["sync"]),
+                                       _p(error_word(ch.device)), _p(chain_trace), chain_stages, sms, _stream())
+            _ok(rc, "linear_chain")
+
+
 # --------------------------------------------------------------------------- many-row products on tcgen05
 GEMM_PLAIN, GEMM_SWIGLU = 0, 1
 _gemm_maps = {}
@@ -722,6 +915,7 @@ def gemm_tc_pays(x: torch.Tensor, weight: torch.Tensor, mode: int = GEMM_PLAIN) 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, mode: int = GEMM_PLAIN) -> torch.Tensor:
     """x . weight^T on the tcgen05 tensor cores (TMA-fed, float sums in tensor memory), bfloat16 out.
     ``GEMM_SWIGLU``: weight = [gate rows; up rows]; the result is silu(x . gate^T) * (x . up^T)."""
+    flush_chain()
     if not gemm_tc_ok(x, weight, mode):
         raise KernelError("the tcgen05 product takes contiguous bfloat16 [M, K] and [N, K] with K a multiple of 8")
     m, k = x.shape
@@ -753,22 +947,23 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x[M, K] . weight[N, K]^T, no bias.
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           lazy: bool = False) -> torch.Tensor:
+    """x[M, K] . weight[N, K]^T, no bias.  ``lazy``: see ``few_row_linear``.
 
-    float32 x float32: this package's 32-bit kernel.  bfloat16 x bfloat16: cuBLAS
-    with float accumulation.  A weight that the checkpoint keeps in float32 under a
-    bfloat16 engine is multiplied in 32-bit (the activations are widened first).
+    float32 x float32: this package's 32-bit kernel.  bfloat16 x bfloat16: few rows (see ``few_row_takes``) on
+    this package's few-row kernels, more on cuBLAS with float accumulation.  Mixed dtypes are multiplied in
+    32-bit (the narrower operand is widened first).
     """
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32 and weight.dtype == torch.float32:
         return cast(gemm_f32(x, weight), out_dtype)
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        if out_dtype in (torch.bfloat16, torch.float32) and x.dim() == 2 and x.is_contiguous() and x.is_cuda:
+            mode = EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16
+            if few_row_takes(x.shape[0], weight, x.dtype, mode):
+                return few_row_linear(x, weight, mode, lazy=lazy)
         _cuda(x, weight)
-        if out_dtype in (torch.bfloat16, torch.float32) and x.dim() == 2 and x.is_contiguous() \
-                and few_row_pays(x.shape[0], weight, x.dtype,
-                                 EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16):
-            return skinny_linear(x, weight, EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16)
         if out_dtype == torch.bfloat16:
             return torch.mm(x, weight.t())
         return torch.mm(x, weight.t(), out_dtype=out_dtype)

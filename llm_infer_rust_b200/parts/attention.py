@@ -41,6 +41,7 @@ class GQAttention(Part):
     model's position encoding.
     """
     category = "mixer"
+    chainable = True          # reads its input through ops.* only, and may return a product that still waits (ops.few_row_linear)
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -77,7 +78,7 @@ class GQAttention(Part):
 
     def takes_pending(self, tokens: int) -> bool:
         """Whether a step of ``tokens`` tokens runs the input norm as the prologue of the QKV product."""
-        return ops.few_row_pays(tokens, self.params["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d, fused_norm=True)
+        return ops.few_row_takes(tokens, self.params["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d)
 
     def forward(self, x, ctx, cache):
         p = self.params
@@ -85,14 +86,13 @@ class GQAttention(Part):
         rope = self.rope
         q = torch.empty((tokens, self.nh * self.d), dtype=x.dtype, device=x.device)
         slots = ctx.slots[cache.group] if cache.writes else None
-        if ops.few_row_pays(tokens, p["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d,
-                            fused_norm=isinstance(x, ops.PendingNorm)):
+        if ops.few_row_takes(tokens, p["qkv_proj"], self.env.dtype, ops.EPI_QKV, self.d):
             # few tokens: norm (if pending), projection, per-head norm, rotation and cache store in one kernel
-            ops.skinny_linear(x, p["qkv_proj"], ops.EPI_QKV, qkv=dict(
+            ops.few_row_linear(x, p["qkv_proj"], ops.EPI_QKV, qkv=dict(
                 head_dim=self.d, num_heads=self.nh, num_kv_heads=self.nkv, q_out=q, k_cache=cache.k, v_cache=cache.v,
                 q_weight=p.get("q_norm"), k_weight=p.get("k_norm"), eps=float(self.qk_eps or 0.0),
                 cos=rope.cos if rope else None, sin=rope.sin if rope else None,
-                rot_dim=rope.rot_dim if rope else 0, positions=ctx.positions, slots=slots))
+                rot_dim=rope.rot_dim if rope else 0, positions=ctx.positions, slots=slots), lazy=True)
         else:
             if isinstance(x, ops.PendingNorm):
                 x = x.materialize()
@@ -116,7 +116,7 @@ class GQAttention(Part):
             ops.decode_attention(q, cache.k, cache.v, out, scratch, ctx.block_tables[g], ctx.cu_q,
                                  ctx.kv_len, ctx.decode_rows, ctx.num_decode, self.nh, self.nkv, self.d,
                                  page, self.window, self.scale, splits)
-        return ops.linear(out, p["o_proj"])
+        return ops.linear(out, p["o_proj"], lazy=True)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -1,6 +1,7 @@
 """Arrangements of a layer's parts."""
 from __future__ import annotations
 
+from ..kernels import ops
 from .registry import build_part, register_part
 
 
@@ -32,17 +33,32 @@ class PreNormDeferredAdd:
         takes = getattr(consumer, "takes_pending", None)
         return hasattr(norm, "pending_add") and takes is not None and takes(tokens)
 
+    @staticmethod
+    def _settle(part):
+        """Products of few rows may wait to be launched together (``ops.few_row_linear``).  A part that says
+        ``chainable = True`` touches activations through ``ops`` alone and may be handed such tensors; before any
+        other part runs, everything that waits is launched."""
+        if not getattr(part, "chainable", False):
+            ops.flush_chain()
+
     def forward(self, h, residual, ctx, cache):
         tokens = h.shape[0]
+        self._settle(self.input_norm)
+        self._settle(self.mixer)
         if residual is None:
             residual = h
-            x = self.input_norm.forward(h)
+            if hasattr(self.input_norm, "pending") and self._fuses(self.input_norm, self.mixer, tokens):
+                x = self.input_norm.pending(h)
+            else:
+                x = self.input_norm.forward(h)
         elif self._fuses(self.input_norm, self.mixer, tokens):
             x = self.input_norm.pending_add(h, residual)
             residual = x.residual_out
         else:
             x = self.input_norm.forward_add(h, residual, out=h)
         a = self.mixer.forward(x, ctx, cache)
+        self._settle(self.post_mixer_norm)
+        self._settle(self.feed_forward)
         if self._fuses(self.post_mixer_norm, self.feed_forward, tokens):
             x = self.post_mixer_norm.pending_add(a, residual)
             residual = x.residual_out

@@ -30,6 +30,7 @@ class LinearHead(Part):
     With ``tied`` and no stored head the weight is the embedding table itself.
     """
     category = "head"
+    chainable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -41,12 +42,12 @@ class LinearHead(Part):
         return {"weight": ParamDecl((self.vocab, self.hidden))}
 
     def takes_pending(self, rows: int) -> bool:
-        return ops.few_row_pays(rows, self.params["weight"], self.env.dtype, ops.EPI_PLAIN_F32, fused_norm=True)
+        return ops.few_row_takes(rows, self.params["weight"], self.env.dtype, ops.EPI_PLAIN_F32)
 
     def forward(self, x):
         if isinstance(x, ops.PendingNorm):
             if self.takes_pending(x.shape[0]):
-                return ops.skinny_linear(x, self.params["weight"], ops.EPI_PLAIN_F32)
+                return ops.few_row_linear(x, self.params["weight"], ops.EPI_PLAIN_F32, lazy=True)
             x = x.materialize()
         return ops.linear(x, self.params["weight"], out_dtype=torch.float32)
 

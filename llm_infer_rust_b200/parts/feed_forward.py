@@ -13,6 +13,7 @@ class SwiGLU(Part):
     src/layers/mlp.rs:7-25, packing src/models/qwen3/model.rs:577-586).
     """
     category = "feed_forward"
+    chainable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -25,13 +26,13 @@ class SwiGLU(Part):
 
     def takes_pending(self, tokens: int) -> bool:
         """Whether a step of ``tokens`` tokens runs the norm before it as the prologue of the gate/up product."""
-        return ops.few_row_pays(tokens, self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU, fused_norm=True)
+        return ops.few_row_takes(tokens, self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU)
 
     def forward(self, x):
-        if ops.few_row_pays(x.shape[0], self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU,
-                            fused_norm=isinstance(x, ops.PendingNorm)):
+        if ops.few_row_takes(x.shape[0], self.params["gate_up_proj"], self.env.dtype, ops.EPI_SWIGLU):
             # few tokens: norm (if pending), gate and up projections and silu(gate) * up in one kernel
-            return ops.linear(ops.skinny_linear(x, self.params["gate_up_proj"], ops.EPI_SWIGLU), self.params["down_proj"])
+            return ops.linear(ops.few_row_linear(x, self.params["gate_up_proj"], ops.EPI_SWIGLU, lazy=True),
+                              self.params["down_proj"], lazy=True)
         if isinstance(x, ops.PendingNorm):
             x = x.materialize()
         if ops.gemm_tc_pays(x, self.params["gate_up_proj"], ops.GEMM_SWIGLU):

@@ -6,6 +6,7 @@ from typing import Dict, List
 import torch
 
 from ..config.spec import ModelSpec
+from ..kernels import ops
 from .base import BuildEnv, Part
 from .registry import build_part
 
@@ -83,10 +84,14 @@ class DecoderModel:
         for e, entry in enumerate(self.run_list):
             h, residual = self.blocks[entry.layer].forward(h, residual, ctx, caches[e])
         takes = getattr(self.lm_head, "takes_pending", None)
+        if not (getattr(self.final_norm, "chainable", False) and getattr(self.lm_head, "chainable", False)):
+            ops.flush_chain()
         if residual is None:
             x = self.final_norm.forward(h, rows=ctx.logit_rows)
         elif hasattr(self.final_norm, "pending_add") and takes is not None and takes(ctx.num_logits):
             x = self.final_norm.pending_add(h, residual, rows=ctx.logit_rows, write_residual=False)
         else:
             x = self.final_norm.forward_add(h, residual, rows=ctx.logit_rows, write_residual=False)
-        return self.lm_head.forward(x)
+        logits = self.lm_head.forward(x)
+        ops.flush_chain()                 # nothing waits when the step's logits are handed out
+        return logits

@@ -14,6 +14,7 @@ class RMSNorm(Part):
     src/layers/fused_ops.cu:49-106).
     """
     category = "norm"
+    chainable = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -35,6 +36,11 @@ class RMSNorm(Part):
         The new residual will be in ``.residual_out`` of the result (``residual`` itself is left alone)."""
         return ops.PendingNorm(x, residual, self.params["weight"], self.eps, rows=rows,
                                write_residual=write_residual)
+
+
+    def pending(self, x, rows=None):
+        """The plain norm of ``x``, not run yet (for a consumer that ``takes_pending``)."""
+        return ops.PendingNorm(x, None, self.params["weight"], self.eps, rows=rows, write_residual=False)
 
 
 register_part("norm", "rms_norm", RMSNorm)
