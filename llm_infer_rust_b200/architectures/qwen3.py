@@ -54,6 +54,7 @@ def qwen3_weight_plan(c: Qwen3Config) -> List[WeightBinding]:
 
 QWEN3 = Architecture(name=Qwen3Config.architecture, model_type=Qwen3Config.model_type,
                      parse_config=Qwen3Config.parse, model_spec=Qwen3Config.model_spec,
-                     weight_plan=qwen3_weight_plan)
+                     weight_plan=qwen3_weight_plan, checkpoint_dtype=lambda c: c.checkpoint_dtype,
+                     stop_ids=lambda c: c.eos_token_ids)
 
 register_architecture(QWEN3, replace=True)

@@ -170,7 +170,7 @@ class Qwen3Config:
                 "num_kv_heads": self.num_key_value_heads, "head_dim": self.head_dim,
                 "qk_norm_eps": self.rms_norm_eps, "window": window,
                 "softmax_scale": 1.0 / math.sqrt(self.head_dim), "position_encoding": "rope"})
-            layers.append(LayerSpec(PartSpec("pre_norm_deferred_add"), mixer, ffn, norm))
+            layers.append(LayerSpec.pre_norm(PartSpec("pre_norm_deferred_add"), mixer, ffn, norm))
         spec = ModelSpec(
             architecture=self.architecture, vocab_size=self.vocab_size,
             hidden_size=self.hidden_size, max_positions=self.max_position_embeddings,

@@ -8,7 +8,7 @@ run time: ``register_architecture`` is all that a new architecture needs.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List
+from typing import Any, Callable, Dict, List, Sequence
 
 from .spec import ConfigError, ModelSpec
 
@@ -20,6 +20,10 @@ class Architecture:
     parse_config: Callable[[dict], Any]           # raw config.json -> typed configuration
     model_spec: Callable[[Any], ModelSpec]        # typed configuration -> parts and run list
     weight_plan: Callable[[Any], List[Any]]       # typed configuration -> WeightBinding list
+    # typed configuration -> the dtype its checkpoint declares ("float32", "bfloat16", "float16"): the engine's "auto"
+    checkpoint_dtype: Callable[[Any], str] = lambda config: "bfloat16"
+    # typed configuration -> token ids that end a generation
+    stop_ids: Callable[[Any], Sequence[int]] = lambda config: ()
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}

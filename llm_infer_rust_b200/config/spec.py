@@ -30,11 +30,25 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """The parts of one layer.  ``block`` names their arrangement."""
+    """The parts of one layer, by name.  ``block`` names their arrangement and says which names it reads: the
+    shipped ``pre_norm_deferred_add`` reads ``mixer``, ``feed_forward``, ``input_norm`` and ``post_mixer_norm``;
+    an arrangement with other norm sites, four norms or two mixers reads other names, and nothing else changes."""
     block: PartSpec
-    mixer: PartSpec
-    feed_forward: PartSpec
-    norm: PartSpec
+    parts: Mapping[str, PartSpec]
+
+    def __getitem__(self, name: str) -> PartSpec:
+        try:
+            return self.parts[name]
+        except KeyError:
+            raise ConfigError(f"the layer has no part named {name!r} (block {self.block.kind!r} asked for it); "
+                              f"it has {sorted(self.parts)}") from None
+
+    @staticmethod
+    def pre_norm(block: PartSpec, mixer: PartSpec, feed_forward: PartSpec, input_norm: PartSpec,
+                 post_mixer_norm: Optional[PartSpec] = None) -> "LayerSpec":
+        """The usual decoder layer: a mixer and a feed-forward, each behind a norm (the same kind unless given)."""
+        return LayerSpec(block, {"mixer": mixer, "feed_forward": feed_forward, "input_norm": input_norm,
+                                 "post_mixer_norm": post_mixer_norm or input_norm})
 
 
 @dataclass(frozen=True)

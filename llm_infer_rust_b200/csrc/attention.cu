@@ -1,9 +1,12 @@
-// Causal grouped-query attention over the paged cache, for one head size
-// (compile with -DHEAD_DIM=<multiple of 16>): a kernel for portions of prompts
-// (many query positions per row) and a split-KV kernel for single decoded
+// Causal grouped-query attention over the paged cache, for head sizes up to
+// HEAD_DIM (compile with -DHEAD_DIM=<multiple of 16>): a kernel for portions of
+// prompts (many query positions per row) and a split-KV kernel for single decoded
 // tokens, both for float and bfloat16 caches.  These are the all-sizes CUDA-core
 // kernels: they serve the float32 engine and are the reference point of the
-// tensor-core kernels.
+// tensor-core kernels.  The real head size `hd` (any even number up to HEAD_DIM; the
+// reference's configuration allows every even head size: src/models/qwen3/config.rs:160-162)
+// is a run-time argument: rows of q, the cache and the output are `hd` wide, the tiles
+// in shared memory HEAD_DIM wide with zeros beyond `hd`.
 //
 // Semantics (reference: src/models/attention/backend.rs:1455-1498): query head h
 // reads KV head h / (nh / nkv); score = q.k / sqrt(d) (the scale is a
@@ -135,26 +138,46 @@ __device__ __forceinline__ void warp_key_block(const T* ks, const T* vs, const f
 // with `nthreads` threads (thread index `tid`); rows at or beyond kv_end become zeros.
 template <typename T>
 __device__ __forceinline__ void load_key_block(T* dst, const T* __restrict__ cache, const int* __restrict__ table,
-                                               int page_size, int nkv, int kvh, int first_key, int kv_end,
+                                               int page_size, int nkv, int kvh, int first_key, int kv_end, int hd,
                                                int tid, int nthreads) {
   using G = RowGeom<T>;
-  for (int c = tid; c < KB * G::CHUNKS; c += nthreads) {
-    const int r = c / G::CHUNKS, part = c - r * G::CHUNKS;
-    const int key = first_key + r;
-    const bool valid = key < kv_end;
-    const T* src = cache;
-    if (valid) {
-      const int page = table[key / page_size];       // cache[page][kv head][offset in page][D]
-      const size_t row = (static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size;
-      src = cache + row * D + part * G::CHUNK;
+  if (hd % G::CHUNK == 0) {
+    // rows start on 16-byte boundaries: asynchronous 16-byte copies, zeros beyond the row and beyond the sequence
+    const int row_chunks = hd / G::CHUNK;
+    for (int c = tid; c < KB * G::CHUNKS; c += nthreads) {
+      const int r = c / G::CHUNKS, part = c - r * G::CHUNKS;
+      const int key = first_key + r;
+      const bool valid = key < kv_end && part < row_chunks;
+      const T* src = cache;
+      if (valid) {
+        const int page = table[key / page_size];       // cache[page][kv head][offset in page][hd]
+        const size_t row = (static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size;
+        src = cache + row * hd + part * G::CHUNK;
+      }
+      cp_async16(dst + r * G::STRIDE + part * G::CHUNK, src, valid);
     }
-    cp_async16(dst + r * G::STRIDE + part * G::CHUNK, src, valid);
+  } else {
+    // an even head size whose rows are not 16-byte aligned: pairs of elements with plain loads
+    for (int c = tid; c < KB * (D / 2); c += nthreads) {
+      const int r = c / (D / 2), pair = c - r * (D / 2);
+      const int key = first_key + r;
+      T a = from_f32<T>(0.0f), b = a;
+      if (key < kv_end && 2 * pair < hd) {
+        const int page = table[key / page_size];
+        const size_t row = (static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size;
+        a = cache[row * hd + 2 * pair];
+        b = cache[row * hd + 2 * pair + 1];
+      }
+      dst[r * G::STRIDE + 2 * pair] = a;
+      dst[r * G::STRIDE + 2 * pair + 1] = b;
+    }
   }
 }
 
 // ------------------------------------------------------------------ prompt portions
-// grid (query tiles, nkv, prefill rows); 8 warps; a tile holds `tile_tokens` consecutive query
-// positions of one row and all `group` query heads of one KV head: tile_tokens * group <= 32 vectors.
+// grid (query tiles, nkv * head chunks, prefill rows); 8 warps; a tile holds `tile_tokens` consecutive query
+// positions of one row and up to 32 of the `group` query heads of one KV head (head chunk hc holds heads
+// 32 hc ..): tile_tokens * heads <= 32 vectors.
 constexpr int PF_WARPS = 8;
 
 template <typename T>
@@ -163,7 +186,7 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                          T* __restrict__ out, const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                          const int* __restrict__ prefix_len, const int* __restrict__ rows, int nh, int nkv,
-                         int page_size, int window, float scale, int tile_tokens) {
+                         int page_size, int window, float scale, int tile_tokens, int head_chunks, int hd) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [32][D]
@@ -172,8 +195,9 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   T* vs = ks + KB * G::STRIDE;
 
   const int row = rows[blockIdx.z];
-  const int kvh = blockIdx.y;
-  const int group = nh / nkv;
+  const int kvh = blockIdx.y / head_chunks, hc = blockIdx.y - kvh * head_chunks;
+  const int head_base = kvh * (nh / nkv) + hc * 32;                      // first query head of this CTA
+  const int group = min(32, nh / nkv - hc * 32);                         // query heads of this CTA
   const int q_begin = cu_q[row], q_len = cu_q[row + 1] - q_begin;
   const int tok0 = blockIdx.x * tile_tokens;
   if (tok0 >= q_len) return;
@@ -190,9 +214,9 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   for (int i = threadIdx.x; i < 32 * D; i += blockDim.x) {
     const int v = i / D, dim = i - v * D;
     float val = 0.0f;
-    if (v < nvec) {
-      const int tok = v / group, head = kvh * group + v % group;
-      val = to_f32<T>(q[(static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D + dim]) * scale;
+    if (v < nvec && dim < hd) {
+      const int tok = v / group, head = head_base + v % group;
+      val = to_f32<T>(q[(static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * hd + dim]) * scale;
     }
     qs[i] = val;
   }
@@ -208,8 +232,8 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   st.init();
   for (int kb = k_begin; kb < kv_end; kb += KB) {
     __syncthreads();                                   // the previous block is no longer read
-    load_key_block<T>(ks, k_cache, table, page_size, nkv, kvh, kb, kv_end, threadIdx.x, blockDim.x);
-    load_key_block<T>(vs, v_cache, table, page_size, nkv, kvh, kb, kv_end, threadIdx.x, blockDim.x);
+    load_key_block<T>(ks, k_cache, table, page_size, nkv, kvh, kb, kv_end, hd, threadIdx.x, blockDim.x);
+    load_key_block<T>(vs, v_cache, table, page_size, nkv, kvh, kb, kv_end, hd, threadIdx.x, blockDim.x);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
@@ -221,13 +245,13 @@ prefill_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
   for (int v = 0; v < NV; ++v) {
     const int vec = warp * NV + v;
     if (vec >= nvec) continue;
-    const int tok = vec / group, head = kvh * group + vec % group;
-    T* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * D;
+    const int tok = vec / group, head = head_base + vec % group;
+    T* dst = out + (static_cast<size_t>(q_begin + tok0 + tok) * nh + head) * hd;
     const float inv = st.l[v] > 0.0f ? 1.0f / st.l[v] : 0.0f;
 #pragma unroll
     for (int k = 0; k < PAIRS; ++k) {
       const int dim = 2 * lane + 64 * k;
-      if (dim < D) {
+      if (dim < hd) {
         dst[dim] = from_f32<T>(st.acc[v][2 * k] * inv);
         dst[dim + 1] = from_f32<T>(st.acc[v][2 * k + 1] * inv);
       }
@@ -248,7 +272,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_len, const int* __restrict__ rows, int nh, int nkv,
-                        int page_size, int window, float scale, int vec_groups, int stages) {
+                        int page_size, int window, float scale, int vec_groups, int stages, int hd) {
   using G = RowGeom<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* qs = reinterpret_cast<float*>(smem_raw);                        // [NV][D]
@@ -274,7 +298,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < NV * D; i += blockDim.x) {
     const int v = i / D, dim = i - v * D;
-    qs[i] = v < nvec ? to_f32<T>(q[(static_cast<size_t>(tok) * nh + head0 + v) * D + dim]) * scale : 0.0f;
+    qs[i] = (v < nvec && dim < hd) ? to_f32<T>(q[(static_cast<size_t>(tok) * nh + head0 + v) * hd + dim]) * scale : 0.0f;
   }
   __syncthreads();
   int qpos[NV];
@@ -290,8 +314,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   for (int s = 0; s < stages - 1; ++s) {
     if (issue < blk_hi) {
       T* t = my_tiles + s * tile_elems;
-      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, lane, 32);
-      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, lane, 32);
+      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
+      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
     }
     cp_async_commit();
     issue += DEC_WARPS;
@@ -302,16 +326,16 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
       const int s_issue = (stage + stages - 1) % stages;
       if (issue < blk_hi) {
         T* t = my_tiles + s_issue * tile_elems;
-        load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, lane, 32);
-        load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, lane, 32);
+        load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
+        load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + issue * KB, kv_end, hd, lane, 32);
       }
       cp_async_commit();
       issue += DEC_WARPS;
       cp_async_wait<1>();          // stages is 1 or 2: all but the newest group have landed
     } else {
       T* t = my_tiles;
-      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, lane, 32);
-      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, lane, 32);
+      load_key_block<T>(t, k_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd, lane, 32);
+      load_key_block<T>(t + KB * G::STRIDE, v_cache, table, page_size, nkv, kvh, k_begin + blk * KB, kv_end, hd, lane, 32);
       cp_async_commit();
       cp_async_wait<0>();
     }
@@ -354,7 +378,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     }
     const int head = head0 + v;
     if (splits == 1) {
-      out[(static_cast<size_t>(tok) * nh + head) * D + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
+      if (dim < hd) out[(static_cast<size_t>(tok) * nh + head) * hd + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
     } else {
       const size_t slot = (static_cast<size_t>(blockIdx.z) * nh + head) * splits + split;
       part_acc[slot * D + dim] = o;
@@ -367,13 +391,13 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                     const float* __restrict__ part_ml, const int* __restrict__ cu_q,
-                                    const int* __restrict__ rows, int nh, int splits) {
+                                    const int* __restrict__ rows, int nh, int splits, int hd) {
   const int head = blockIdx.y;
   const int tok = cu_q[rows[blockIdx.x]];
   const size_t base = (static_cast<size_t>(blockIdx.x) * nh + head) * splits;
   float m = -INFINITY;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-  for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
+  for (int dim = threadIdx.x; dim < hd; dim += blockDim.x) {
     float l = 0.0f, o = 0.0f;
     if (m != -INFINITY) {
       for (int s = 0; s < splits; ++s) {
@@ -382,7 +406,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, const float* __restrict
         o += part_acc[(base + s) * D + dim] * f;
       }
     }
-    out[(static_cast<size_t>(tok) * nh + head) * D + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
+    out[(static_cast<size_t>(tok) * nh + head) * hd + dim] = from_f32<T>(l > 0.0f ? o / l : 0.0f);
   }
 }
 
@@ -391,11 +415,11 @@ template <typename T>
 static int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_table,
                           int table_stride, const int* cu_q, const int* kv_len, const int* prefix_len,
                           const int* rows, int n_rows, int max_q_len, int nh, int nkv, int page_size, int window,
-                          float scale, cudaStream_t stream) {
+                          float scale, int hd, cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
-  if (group > 32) return B200_BAD_SIZE;
-  const int tile_tokens = 32 / group;
+  const int head_chunks = (group + 31) / 32;                  // more than 32 query heads per KV head: several CTAs
+  const int tile_tokens = group >= 32 ? 1 : 32 / group;
   const size_t smem = (32 * D + PF_WARPS * KB * NV) * sizeof(float) + 2 * KB * G::STRIDE * sizeof(T);
   static bool configured = false;
   if (!configured) {
@@ -404,10 +428,12 @@ static int launch_prefill(const void* q, const void* kc, const void* vc, void* o
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid((max_q_len + tile_tokens - 1) / tile_tokens, nkv, n_rows);
+  if (static_cast<long long>(nkv) * head_chunks > 65535 || n_rows > 65535) return B200_BAD_SIZE;
+  dim3 grid((max_q_len + tile_tokens - 1) / tile_tokens, nkv * head_chunks, n_rows);
   prefill_attention_kernel<T><<<grid, PF_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
-      block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size, window, scale, tile_tokens);
+      block_table, table_stride, cu_q, kv_len, prefix_len, rows, nh, nkv, page_size, window, scale, tile_tokens,
+      head_chunks, hd);
   return b200_check_launch();
 }
 
@@ -415,7 +441,7 @@ template <typename T>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_acc, float* part_ml,
                          const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                          const int* rows, int n_rows, int nh, int nkv, int page_size, int window, float scale,
-                         int splits, cudaStream_t stream) {
+                         int splits, int hd, cudaStream_t stream) {
   using G = RowGeom<T>;
   const int group = nh / nkv;
   const int vec_groups = (group + NV - 1) / NV;
@@ -441,12 +467,12 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
   decode_attention_kernel<T, DEC_WARPS><<<grid, DEC_WARPS * 32, smem, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out),
       part_acc, part_ml, block_table, table_stride, cu_q, kv_len, rows, nh, nkv, page_size, window, scale,
-      vec_groups, stages);
+      vec_groups, stages, hd);
   int rc = b200_check_launch();
   if (rc != 0 || splits == 1) return rc;
   dim3 mgrid(n_rows, nh);
   decode_merge_kernel<T><<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(static_cast<T*>(out), part_acc, part_ml, cu_q,
-                                                                   rows, nh, splits);
+                                                                   rows, nh, splits, hd);
   return b200_check_launch();
 }
 
@@ -457,20 +483,22 @@ B200_EXPORT int b200_prefill_attention(const void* q, const void* k_cache, const
                                        const int* block_table, int table_stride, const int* cu_q,
                                        const int* kv_len, const int* prefix_len, const int* rows, int n_rows,
                                        int max_q_len, int nh, int nkv, int page_size, int window, float scale,
-                                       int dtype, cudaStream_t stream) {
+                                       int dtype, int head_dim, cudaStream_t stream) {
   if (n_rows <= 0 || max_q_len <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return B200_BAD_SIZE;
+  if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
   if (dtype == B200_F32)
     return launch_prefill<float>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len, prefix_len,
-                                 rows, n_rows, max_q_len, nh, nkv, page_size, window, scale, stream);
+                                 rows, n_rows, max_q_len, nh, nkv, page_size, window, scale, head_dim, stream);
   if (dtype == B200_BF16)
     return launch_prefill<__nv_bfloat16>(q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_len,
                                          prefix_len, rows, n_rows, max_q_len, nh, nkv, page_size, window, scale,
-                                         stream);
+                                         head_dim, stream);
   return B200_BAD_DTYPE;
 }
 
-// Scratch floats that b200_decode_attention needs for (n_rows, nh, splits): acc then (max, sum).
+// Scratch floats that b200_decode_attention needs for (n_rows, nh, splits): acc then (max, sum); rows of HEAD_DIM
+// floats whatever the real head size.
 B200_EXPORT long long b200_decode_scratch_floats(int n_rows, int nh, int splits) {
   return splits <= 1 ? 0 : static_cast<long long>(n_rows) * nh * splits * (D + 2);
 }
@@ -480,17 +508,18 @@ B200_EXPORT int b200_decode_attention(const void* q, const void* k_cache, const 
                                       float* scratch, const int* block_table, int table_stride,
                                       const int* cu_q, const int* kv_len, const int* rows, int n_rows, int nh,
                                       int nkv, int page_size, int window, float scale, int splits, int dtype,
-                                      cudaStream_t stream) {
+                                      int head_dim, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || splits <= 0) return B200_BAD_SIZE;
+  if (head_dim <= 0 || head_dim > D || (head_dim & 1)) return B200_BAD_SIZE;
   float* part_acc = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
   if (dtype == B200_F32)
     return launch_decode<float>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride, cu_q,
-                                kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, stream);
+                                kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, head_dim, stream);
   if (dtype == B200_BF16)
     return launch_decode<__nv_bfloat16>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride,
                                         cu_q, kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits,
-                                        stream);
+                                        head_dim, stream);
   return B200_BAD_DTYPE;
 }

@@ -85,7 +85,7 @@ B200_EXPORT int b200_decode_attention_static(const void* q, const void* k_cache,
   float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
   if (dtype == B200_F32)
     return launch_decode<float>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride, cu_q,
-                                kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, stream);
+                                kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, D, stream);
   return launch_decode<__nv_bfloat16>(q, k_cache, v_cache, out, part_acc, part_ml, block_table, table_stride, cu_q,
-                                      kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, stream);
+                                      kv_len, rows, n_rows, nh, nkv, page_size, window, scale, splits, D, stream);
 }

@@ -46,6 +46,7 @@ PYBIND11_MODULE(_host_runtime, m) {
       .def("acquire", &CacheManager::acquire, py::arg("id"), py::arg("capacity_tokens"), py::arg("max_step_tokens"))
       .def("open", &CacheManager::open)
       .def("grow", &CacheManager::grow)
+      .def("grow_all", &CacheManager::grow_all)
       .def("advance", &CacheManager::advance)
       .def("release", &CacheManager::release)
       .def("length", &CacheManager::length)
@@ -117,6 +118,7 @@ PYBIND11_MODULE(_host_runtime, m) {
       .def("params_of", &Scheduler::params_of)
       .def("commit_step", &Scheduler::commit_step)
       .def("fail_step", &Scheduler::fail_step)
+      .def("rollback_step", &Scheduler::rollback_step)
       .def("drain_outbox", &Scheduler::drain_outbox)
       .def("num_pending", &Scheduler::num_pending)
       .def("num_running", &Scheduler::num_running)

@@ -109,6 +109,28 @@ bool CacheManager::grow(int64_t id, int new_length) {
   return true;
 }
 
+int CacheManager::grow_all(const std::vector<int64_t>& ids, const std::vector<int>& new_lengths) {
+  if (ids.size() != new_lengths.size()) throw std::invalid_argument("one length for every request");
+  for (size_t i = 0; i < ids.size(); ++i)
+    for (size_t j = 0; j < i; ++j)
+      if (ids[j] == ids[i]) throw std::invalid_argument("a request appears twice in one step");
+  std::vector<int> beyond(specs_.size(), 0);      // pages beyond the requests' own promises, taken so far
+  for (size_t i = 0; i < ids.size(); ++i) {
+    const RequestCache& rc = requests_.at(ids[i]);
+    for (size_t g = 0; g < specs_.size(); ++g) {
+      const GroupPages& gp = rc.groups[g];
+      int want = ceil_div(new_lengths[i], specs_[g].page_size);
+      int have = static_cast<int>(gp.table.size());
+      int need = std::max(0, want - std::max(have, gp.first_live));
+      beyond[g] += std::max(0, need - gp.promised);
+      if (beyond[g] > unpromised_pages(static_cast<int>(g))) return static_cast<int>(i);
+    }
+  }
+  for (size_t i = 0; i < ids.size(); ++i)
+    if (!grow(ids[i], new_lengths[i])) throw std::logic_error("page accounting is broken: a checked growth failed");
+  return -1;
+}
+
 void CacheManager::advance(int64_t id, int new_length) {
   RequestCache& rc = requests_.at(id);
   if (new_length < rc.length) throw std::invalid_argument("a request cannot shrink");

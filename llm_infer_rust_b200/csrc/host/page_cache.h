@@ -88,6 +88,9 @@ class CacheManager {
   // Make pages cover positions [0, new_length) (windowed groups: from the
   // first live page).  False, and nothing changed, if a group cannot give them.
   bool grow(int64_t id, int new_length);
+  // The same for several requests at once: either all of them get their pages or nothing changes.  Returns -1, or
+  // the index of the first request for which the free pages do not reach (those before it would fit).
+  int grow_all(const std::vector<int64_t>& ids, const std::vector<int>& new_lengths);
   // The request now holds `new_length` tokens; windowed groups give back the
   // pages that no later query can read.
   void advance(int64_t id, int new_length);

@@ -186,6 +186,23 @@ std::vector<OutputToken> Scheduler::commit_step(const StepPlan& plan, const std:
   return out;
 }
 
+int Scheduler::rollback_step(const StepPlan& plan) {
+  int moved = 0;
+  // last admitted first, each to the front: the queue ends up in arrival order again
+  for (auto e = plan.entries.rbegin(); e != plan.entries.rend(); ++e) {
+    if (e->start != 0) continue;
+    auto it = std::find_if(running_.begin(), running_.end(), [&](const Request& r) { return r.uid == e->uid; });
+    if (it == running_.end() || it->status != Status::Prefilling || it->cursor != 0) continue;
+    Request r = std::move(*it);
+    running_.erase(it);
+    cache_->release(r.uid);
+    r.status = Status::Waiting;
+    pending_.push_front(std::move(r));
+    ++moved;
+  }
+  return moved;
+}
+
 std::vector<OutputToken> Scheduler::fail_step(const StepPlan& plan) {
   std::vector<OutputToken> out;
   for (const PlanEntry& e : plan.entries) {

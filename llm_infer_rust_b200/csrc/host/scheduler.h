@@ -93,6 +93,10 @@ class Scheduler {
   std::vector<OutputToken> commit_step(const StepPlan& plan, const std::vector<int>& sampled);
   // The step failed: every request in it finishes with Error and frees its pages.
   std::vector<OutputToken> fail_step(const StepPlan& plan);
+  // The step could not even be built (nothing of it ran): requests that `plan` admitted give back what they were
+  // promised and return to the head of the queue in their old order; the others stay as they were.  Returns how
+  // many went back (reference: src/scheduler/prefill.rs:65-71, :119-129).
+  int rollback_step(const StepPlan& plan);
   // Results that arose outside a step (aborts at submission or admission).
   std::vector<OutputToken> drain_outbox();
 

@@ -13,6 +13,7 @@ all go through it.
 """
 from __future__ import annotations
 
+import logging
 from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -32,6 +33,7 @@ from ..weights.random_init import bind_random_weights
 from .context import StepContext, context_from_layout
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+log = logging.getLogger("llm_infer_rust_b200")
 
 
 @dataclass
@@ -135,12 +137,24 @@ class Engine:
                  cuda_graph_bs: Optional[int] = 0, prefill_cuda_graph_max_tokens: int = 0,
                  eos_token_ids: Optional[Sequence[int]] = None, cpu_gpu_overlap: bool = True,
                  seed: int = 0, log_level: str = "info", random_weights_config: Optional[dict] = None,
-                 random_weights_seed: int = 0):
+                 random_weights_seed: int = 0, keep_float32_tensors: Optional[bool] = None):
         """``model_path``: a folder with config.json and model.safetensors.  With ``model_path`` None and
         ``random_weights_config`` (the keys of a config.json) the weights are drawn on the device from
-        ``random_weights_seed`` and no file is read: for sizes whose checkpoint would take long to write."""
+        ``random_weights_seed`` and no file is read: for sizes whose checkpoint would take long to write.
+        ``keep_float32_tensors``: what a bfloat16 engine does with tensors stored in 32-bit (None: they stay float32
+        in a checkpoint that declares itself 16-bit and are converted otherwise; see weights/loader.py).
+        ``log_level``: error, warn(ing), info, debug or trace, for the package's logger."""
         self.model_path = model_path
         self.log_level = log_level
+        level = {"error": logging.ERROR, "warn": logging.WARNING, "warning": logging.WARNING, "info": logging.INFO,
+                 "debug": logging.DEBUG, "trace": logging.DEBUG}.get(str(log_level).lower())
+        if level is None:
+            raise ConfigError(f"log level {log_level!r} is refused: error, warn, info, debug and trace are known")
+        log.setLevel(level)
+        if not log.handlers and not logging.getLogger().handlers:          # (an application's own handlers win)
+            handler = logging.StreamHandler()
+            handler.setFormatter(logging.Formatter("[llm_infer_rust_b200] %(levelname)s %(message)s"))
+            log.addHandler(handler)
         if model_path is None and random_weights_config is None:
             raise ConfigError("a model folder (or random_weights_config) is needed")
         raw = dict(random_weights_config) if model_path is None else read_config_json(model_path)
@@ -151,7 +165,7 @@ class Engine:
 
         self._setup_device(device)
         if dtype == "auto":
-            dtype = getattr(self.config, "checkpoint_dtype", "bfloat16")
+            dtype = self.arch.checkpoint_dtype(self.config)
             dtype = "bfloat16" if dtype == "float16" else dtype
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype {dtype!r} is refused: bfloat16 and float32 are supported")
@@ -185,7 +199,7 @@ class Engine:
                                                       random_weights_seed, self.dtype, self.device)
         else:
             self.loaded_tensors = load_weights(self.model, self.arch.weight_plan(self.config), model_path,
-                                               self.dtype, self.device)
+                                               self.dtype, self.device, keep_float32=keep_float32_tensors)
         unbound = self.model.unbound_parameters()
         if unbound:
             raise RuntimeError(f"the weight plan of {self.arch.name} left parameters unbound: {unbound}")
@@ -202,7 +216,7 @@ class Engine:
         rt = load_host_runtime()
         self._rt = rt
         if eos_token_ids is None:
-            eos_token_ids = getattr(self.config, "eos_token_ids", ())
+            eos_token_ids = self.arch.stop_ids(self.config)
         self.eos_token_ids = tuple(eos_token_ids)
         self.scheduler = rt.Scheduler(self.cache.manager,
                                       rt.SchedulerOptions(max_running_req, max_seq_len, self.max_batch_tokens),
@@ -214,6 +228,7 @@ class Engine:
         self._seeds: Dict[int, int] = {}
         self.cpu_gpu_overlap = bool(cpu_gpu_overlap)
         self._flight: Optional[_Flight] = None          # the step that is already on the GPU (scheduler loop)
+        self._launched = False                          # whether the step being built has put work on the GPU
         self.last_step_error = False
 
         self._graphs: Dict[int, _DecodeGraph] = {}
@@ -296,6 +311,8 @@ class Engine:
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         mgr = self.cache.manager
+        self._launched = False                       # nothing of this step is on the GPU yet
+        new_lengths = []
         for e in entries:
             if len(e.tokens) == 0:
                 raise ValueError("a step entry must bring at least one token")
@@ -303,10 +320,13 @@ class Engine:
             if new_len > self.model.spec.max_positions:
                 raise ValueError(f"request {e.request} would reach {new_len} tokens, beyond the model's "
                                  f"{self.model.spec.max_positions} positions")
-            if not mgr.grow(e.request, new_len):
-                raise MemoryError(f"the cache has no pages left for request {e.request} "
-                                  f"({new_len} tokens); free pages per group: "
-                                  f"{[mgr.free_pages(g) for g in range(mgr.num_groups())]}")
+            new_lengths.append(new_len)
+        # pages for all entries or for none: a step that does not fit leaves every request as it was
+        short = mgr.grow_all([int(e.request) for e in entries], new_lengths)
+        if short >= 0:
+            raise MemoryError(f"the cache has no pages left for request {entries[short].request} "
+                              f"({new_lengths[short]} tokens) in this step of {len(entries)} entries; nothing was "
+                              f"taken; free pages per group: {[mgr.free_pages(g) for g in range(mgr.num_groups())]}")
         req = self._batch_request(entries)
         decode_only = all(c == 1 for c in req.counts)
         if device_tokens is not None and (not decode_only or device_tokens.numel() != len(entries)
@@ -337,6 +357,7 @@ class Engine:
         if device_tokens is not None:
             dev[layout.off_tokens:layout.off_tokens + layout.num_tokens].copy_(device_tokens, non_blocking=True)
         ctx = self._context(layout, dev, host, layout.max_kv_len)
+        self._launched = True
         return self.model.forward(ctx, self.cache.layer_caches)
 
     def _shape_graph(self, key: tuple) -> Optional[_DecodeGraph]:
@@ -356,37 +377,73 @@ class Engine:
             self._shape_graphs.popitem(last=False)
         return g
 
-    def _step_graph(self, g: _DecodeGraph, req, real_rows: int,
-                    device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _graph_request(self, req, g: _DecodeGraph):
         req.pad_rows_to = g.bucket
         req.fixed_table_width = list(self.table_width)
-        layout = self._rt.plan_batch(self.cache.manager, req)
-        self._meta.reserve(layout.total_ints)
-        turn, host = self._meta.next_host()
-        layout = self._rt.build_batch(self.cache.manager, req, host.numpy())
-        if g.graph is None:
+        return req
+
+    def _capture(self, g: _DecodeGraph, counts: Sequence[int], want_counts: Sequence[int],
+                 want_index: Sequence[int]) -> bool:
+        """Capture ``g`` for a batch of this shape, on throw-away requests: the step that is captured (and the
+        run before it that sizes scratch memory and loads kernels) must not touch a live request, whose cache
+        rows and per-request state would else be written twice for one step.  False (and nothing captured) when
+        the pages or state slots for the throw-away requests are not free right now."""
+        mgr, rt = self.cache.manager, self._rt
+        ids = [-(i + 1) for i in range(len(counts))]
+        opened = []
+        try:
+            for rid in ids:
+                if mgr.has(rid) or mgr.open(rid) != rt.Acquire.Ready:
+                    return False
+                opened.append(rid)
+            if mgr.grow_all(ids, [int(c) for c in counts]) >= 0:
+                return False
+            req = rt.BatchRequest()
+            req.ids, req.counts, req.tokens = ids, [int(c) for c in counts], [0] * int(sum(counts))
+            req.want_counts, req.want_index = [int(c) for c in want_counts], [int(i) for i in want_index]
+            self._graph_request(req, g)
+            layout = rt.plan_batch(mgr, req)
+            self._meta.reserve(layout.total_ints)
+            turn, host = self._meta.next_host()
+            layout = rt.build_batch(mgr, req, host.numpy())
             g.meta = torch.empty(layout.total_ints, dtype=torch.int32, device=self.device)
             self._meta.upload(turn, layout.total_ints, g.meta)
             g.ctx = self._context(layout, g.meta, None, self.max_seq_len)
             # Warm up outside the capture (sizes scratch, loads kernels), then capture.
             side = torch.cuda.Stream(self.device)
             side.wait_stream(torch.cuda.current_stream())
+            before = ops.launch_count()
             with torch.cuda.stream(side):
                 self.model.forward(g.ctx, self.cache.layer_caches)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize(self.device)
-            g.graph = torch.cuda.CUDAGraph()
-            before = ops.launch_count()
-            with ops.graph_capture(g.graph):
+            graph = torch.cuda.CUDAGraph()
+            with ops.graph_capture(graph):
                 g.logits = self.model.forward(g.ctx, self.cache.layer_caches)
-            g.launches = ops.launch_count() - before
-            ops.add_launches(-g.launches)        # captured, not run
+            g.launches = (ops.launch_count() - before) // 2
+            ops.add_launches(-2 * g.launches)    # a warm-up on throw-away rows and a capture: not the model's work
+            g.graph = graph
             g.layout_key = layout.total_ints
-        elif layout.total_ints != g.layout_key:
-            raise RuntimeError("a decode graph was given a batch of another shape than it was captured for")
+            return True
+        finally:
+            for rid in opened:
+                mgr.release(rid)
+
+    def _step_graph(self, g: _DecodeGraph, req, real_rows: int,
+                    device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if g.graph is None and not self._capture(g, req.counts, req.want_counts, req.want_index):
+            return self._step_eager(req, device_tokens)       # no room for the capture now: this step runs as it is
+        self._graph_request(req, g)
+        layout = self._rt.plan_batch(self.cache.manager, req)
+        if layout.total_ints != g.layout_key:
+            raise RuntimeError("a graph was given a batch of another shape than it was captured for")
+        self._meta.reserve(layout.total_ints)
+        turn, host = self._meta.next_host()
+        layout = self._rt.build_batch(self.cache.manager, req, host.numpy())
         self._meta.upload(turn, layout.total_ints, g.meta)
         if device_tokens is not None:
             g.meta[layout.off_tokens:layout.off_tokens + real_rows].copy_(device_tokens, non_blocking=True)
+        self._launched = True
         g.graph.replay()
         ops.add_launches(g.launches)
         return g.logits[:real_rows] if g.bucket else g.logits
@@ -394,21 +451,8 @@ class Engine:
     def capture_graphs(self) -> None:
         """Capture every decode graph bucket now (else each is captured at its first use)."""
         for bucket, g in sorted(self._graphs.items()):
-            if g.graph is not None:
-                continue
-            ids = [-(i + 1) for i in range(bucket)]
-            for rid in ids:
-                self.open_request(rid)
-            try:
-                entries = [StepEntry(rid, [0], [0]) for rid in ids]
-                for e in entries:
-                    if not self.cache.manager.grow(e.request, 1):
-                        raise MemoryError("not enough pages to capture the decode graphs")
-                self._step_graph(g, self._batch_request(entries), bucket)
-                torch.cuda.synchronize(self.device)
-            finally:
-                for rid in ids:
-                    self.close_request(rid)
+            if g.graph is None and not self._capture(g, [1] * bucket, [1] * bucket, [0] * bucket):
+                raise MemoryError(f"not enough free pages or state slots to capture the decode graph of {bucket} rows")
 
     @property
     def last_upload_bytes(self) -> int:
@@ -475,6 +519,14 @@ class Engine:
                 plan = sched.plan_step()
                 out += sched.drain_outbox()
                 if not plan.entries:
+                    if not out and sched.num_pending() and not sched.num_running():
+                        # the head of the queue waits for pages or a slot that no running request will ever free
+                        # (they are held through open_request / step): waiting again would never end
+                        mgr = self.cache.manager
+                        raise MemoryError(f"{sched.num_pending()} requests wait and nothing runs: free pages per group "
+                                          f"{[mgr.free_pages(g) for g in range(mgr.num_groups())]}, free state slots "
+                                          f"{mgr.free_state_slots()}, live requests outside the scheduler {mgr.live_requests()}")
+                    self._forget_finished(out)
                     return out
                 flight = _Flight(plan, None, None)            # (so that a failing launch fails this plan)
                 flight = self._launch(plan, None)
@@ -490,8 +542,12 @@ class Engine:
                 sampled = []
                 self.check_kernel_errors()
         except Exception:
-            self._flight = None                               # its requests are those of this step: they end here
-            out += sched.fail_step(flight.plan)
+            self._flight = None
+            if flight is not None and flight.read is None and flight.ids is None and not self._launched:
+                # the step could not be built and nothing of it ran: what it admitted goes back to the queue's head
+                sched.rollback_step(flight.plan)
+            elif flight is not None:
+                out += sched.fail_step(flight.plan)           # its requests are those of this step: they end here
             self.last_step_error = True
             self._forget_finished(out)
             raise

@@ -62,9 +62,19 @@ def build_dir() -> str:
                 os.remove(probe)
                 _build_dir = preferred
             except OSError:
-                _build_dir = os.path.join(tempfile.gettempdir(),
-                                          f"llm_infer_rust_b200_build_{os.getuid()}")
-                os.makedirs(_build_dir, exist_ok=True)
+                # A read-only checkout: a per-user folder under the temporary directory.  Libraries found there are
+                # loaded as they are, so the folder must be this user's own and closed to everybody else; a folder
+                # of that name that somebody else made (or left open) is not used.
+                shared = os.path.join(tempfile.gettempdir(), f"llm_infer_rust_b200_build_{os.getuid()}")
+                try:
+                    os.makedirs(shared, mode=0o700, exist_ok=True)
+                    st = os.lstat(shared)
+                    import stat
+                    if not stat.S_ISDIR(st.st_mode) or st.st_uid != os.getuid() or (st.st_mode & 0o022):
+                        raise OSError("the build folder is not this user's own")
+                    _build_dir = shared
+                except OSError:
+                    _build_dir = tempfile.mkdtemp(prefix="llm_infer_rust_b200_build_")
         return _build_dir
 
 

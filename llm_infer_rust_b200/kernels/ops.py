@@ -159,11 +159,16 @@ def _elementwise():
     return load_cuda_library("elementwise.cu")
 
 
+def padded_head_dim(head_dim: int) -> int:
+    """The compile-time head size of the all-sizes attention kernels for a real head size: the next multiple of 16."""
+    return -(-head_dim // 16) * 16
+
+
 def _attention(head_dim: int):
-    if head_dim % 16 != 0 or not 16 <= head_dim <= 512:
-        raise KernelError(f"head size {head_dim} is refused: the attention kernels take multiples of 16 "
-                          f"from 16 to 512")
-    return load_cuda_library("attention.cu", {"HEAD_DIM": head_dim})
+    """The all-sizes attention library for a real head size (any even number up to 512)."""
+    if head_dim % 2 != 0 or not 2 <= head_dim <= 512:
+        raise KernelError(f"head size {head_dim} is refused: the attention kernels take even head sizes up to 512")
+    return load_cuda_library("attention.cu", {"HEAD_DIM": padded_head_dim(head_dim)})
 
 
 # --------------------------------------------------------------------------- element-wise
@@ -319,7 +324,7 @@ def prefill_attention(q, k_cache, v_cache, out, block_table, cu_q, kv_len, prefi
     rc = _attention(head_dim).b200_prefill_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(block_table), block_table.shape[-1], _p(cu_q),
         _p(kv_len), _p(prefix_len), _p(rows), n_rows, max_q_len, num_heads, num_kv_heads, page_size,
-        int(window or 0), ctypes.c_float(scale), _code(q), _stream())
+        int(window or 0), ctypes.c_float(scale), _code(q), head_dim, _stream())
     _ok(rc, "prefill_attention")
 
 
@@ -370,7 +375,8 @@ def decode_ctas_per_split(dtype: torch.dtype, n_rows: int, num_heads: int, num_k
 
 
 def decode_scratch_floats(n_rows: int, num_heads: int, head_dim: int, splits: int) -> int:
-    return 0 if splits <= 1 else n_rows * num_heads * splits * (head_dim + 2)
+    """Floats of scratch that decode attention needs (partial outputs are rows of the padded head size)."""
+    return 0 if splits <= 1 else n_rows * num_heads * splits * (padded_head_dim(head_dim) + 2)
 
 
 def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_len, rows, n_rows,
@@ -399,7 +405,7 @@ def decode_attention(q, k_cache, v_cache, out, scratch, block_table, cu_q, kv_le
     rc = _attention(head_dim).b200_decode_attention(
         _p(q), _p(k_cache), _p(v_cache), _p(out), _p(scratch), _p(block_table), block_table.shape[-1],
         _p(cu_q), _p(kv_len), _p(rows), n_rows, num_heads, num_kv_heads, page_size, int(window or 0),
-        ctypes.c_float(scale), splits, _code(q), _stream())
+        ctypes.c_float(scale), splits, _code(q), head_dim, _stream())
     _ok(rc, "decode_attention", 2 if splits > 1 else 1)
 
 

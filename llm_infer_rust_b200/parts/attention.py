@@ -54,11 +54,8 @@ class GQAttention(Part):
         self.scale = float(spec.get("softmax_scale", 1.0 / math.sqrt(self.d)))
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if self.d % 16 or not 16 <= self.d <= 512:
-            raise ValueError(f"head_dim {self.d} is refused: the attention kernels take multiples of 16 "
-                             f"from 16 to 512")
-        if self.nh // self.nkv > 32:
-            raise ValueError("more than 32 query heads per KV head are refused by the attention kernels")
+        if self.d % 2 or not 2 <= self.d <= 512:
+            raise ValueError(f"head_dim {self.d} is refused: the attention kernels take even head sizes up to 512")
         name = spec.get("position_encoding")
         self.rope = env.position_encodings[name] if name else None
 

@@ -18,10 +18,10 @@ class PreNormDeferredAdd:
 
     def __init__(self, layer_spec, env):
         self.spec = layer_spec
-        self.input_norm = build_part("norm", layer_spec.norm, env)
-        self.post_mixer_norm = build_part("norm", layer_spec.norm, env)
-        self.mixer = build_part("mixer", layer_spec.mixer, env)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, env)
+        self.input_norm = build_part("norm", layer_spec["input_norm"], env)
+        self.post_mixer_norm = build_part("norm", layer_spec["post_mixer_norm"], env)
+        self.mixer = build_part("mixer", layer_spec["mixer"], env)
+        self.feed_forward = build_part("feed_forward", layer_spec["feed_forward"], env)
 
     def children(self):
         return {"input_norm": self.input_norm, "mixer": self.mixer,

@@ -176,3 +176,25 @@ def test_random_orders_lose_no_page(seed):
         m.release(rid)
     assert [m.free_pages(g) for g in range(len(pages))] == pages and m.free_state_slots() == 5
     assert m.check() == ""
+
+
+def test_growth_of_a_whole_step_is_all_or_nothing():
+    """A step's entries get their pages together or not at all: an entry that does not fit leaves the ones
+    before it as they were (pages that only a promise covers count for the request that holds the promise)."""
+    m = manager(6, page_size=4)
+    for rid in (1, 2, 3):
+        assert m.open(rid) == rt.Acquire.Ready
+    assert m.grow_all([1, 2], [8, 8]) == -1 and m.free_pages(0) == 2
+    before = [list(m.block_table(r, 0)) for r in (1, 2, 3)]
+    assert m.grow_all([1, 3, 2], [12, 5, 9]) == 1            # 1 + 2 + 1 pages wanted, two are free: request 3 is short
+    assert [list(m.block_table(r, 0)) for r in (1, 2, 3)] == before and m.free_pages(0) == 2 and m.check() == ""
+    assert m.grow_all([1, 3], [12, 3]) == -1 and m.free_pages(0) == 0 and m.check() == ""
+    with pytest.raises(Exception):
+        m.grow_all([1, 1], [13, 14])                         # a request twice in one step
+    with pytest.raises(Exception):
+        m.grow_all([1], [13, 14])
+    # with a promise: request 5's promised pages are its own, request 4 cannot take them
+    p = manager(4, page_size=2)
+    assert p.acquire(5, 6, 6) == rt.Acquire.Ready and p.open(4) == rt.Acquire.Ready
+    assert p.grow_all([4, 5], [4, 6]) == 0 and p.free_pages(0) == 4          # 4 wants two pages, one is unpromised
+    assert p.grow_all([4, 5], [2, 6]) == -1 and p.free_pages(0) == 0 and p.check() == ""

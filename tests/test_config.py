@@ -111,9 +111,9 @@ def test_model_spec_is_data_chosen_layer_by_layer():
     r.update(use_sliding_window=True, sliding_window=8, layer_types=["sliding_attention", "full_attention"])
     spec = Qwen3Config.parse(r).model_spec()
     assert [e.layer for e in spec.run_list] == [0, 1] and all(e.reads is None for e in spec.run_list)
-    assert spec.layers[0].mixer["window"] == 8 and spec.layers[1].mixer["window"] is None
-    assert spec.layers[0].mixer["num_heads"] == 4 and spec.layers[0].mixer["num_kv_heads"] == 2
-    assert spec.layers[0].norm["eps"] == 0.00001
+    assert spec.layers[0]["mixer"]["window"] == 8 and spec.layers[1]["mixer"]["window"] is None
+    assert spec.layers[0]["mixer"]["num_heads"] == 4 and spec.layers[0]["mixer"]["num_kv_heads"] == 2
+    assert spec.layers[0]["post_mixer_norm"]["eps"] == 0.00001
     assert spec.position_encodings["rope"]["theta"] == 1000000.0
     assert spec.lm_head["tied"] is True
 

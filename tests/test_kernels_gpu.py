@@ -275,6 +275,7 @@ QKV_CASES = [  # nh, nkv, d, rot, eps, with_norm
     (4, 2, 16, 16, 1e-6, True), (6, 2, 32, 32, 1e-5, True), (5, 5, 48, 48, 3e-6, True),
     (8, 1, 128, 128, 1e-6, True), (3, 3, 80, 32, 1e-6, True), (2, 1, 64, 64, 1e-6, False),
     (1, 1, 256, 0, 1e-6, True),
+    (3, 1, 40, 40, 1e-6, True), (2, 2, 72, 36, 1e-5, True), (4, 2, 42, 42, 1e-6, False),
 ]
 
 
@@ -367,6 +368,9 @@ ATT_CASES = [  # nh, nkv, d, page, window
     (4, 2, 16, 4, None), (6, 2, 32, 16, None), (5, 5, 48, 8, 40), (8, 1, 128, 16, None),
     (16, 2, 64, 1, 7), (3, 1, 80, 64, None), (2, 2, 256, 16, 33), (32, 8, 128, 16, None),
     (8, 2, 128, 4, None), (16, 4, 128, 64, 100),
+    # any even head size (rows of 80 and 144 bytes in bfloat16, and 84: no 16-byte alignment), and more than 32 query
+    # heads per KV head (the all-sizes kernels serve them in chunks of 32)
+    (4, 2, 40, 8, None), (6, 3, 72, 16, 20), (3, 1, 42, 4, None), (40, 1, 32, 16, None), (66, 2, 16, 8, 9),
 ]
 
 

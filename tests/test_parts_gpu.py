@@ -192,7 +192,7 @@ def test_block_arrangement_defers_the_second_add():
 
     register_part("mixer", "test_doubler", Doubler, replace=True)
     register_part("feed_forward", "test_negate", Negate, replace=True)
-    layer = LayerSpec(spec("pre_norm_deferred_add"), spec("test_doubler"), spec("test_negate"),
+    layer = LayerSpec.pre_norm(spec("pre_norm_deferred_add"), spec("test_doubler"), spec("test_negate"),
                       spec("rms_norm", width=6, eps=1e-6))
     block = build_part("block", layer, env())
     w1, w2 = 1 + 0.1 * rnd(6), 1 + 0.1 * rnd(6, seed=1)

@@ -2,8 +2,8 @@
 
 The tiny configurations of conftest.py are chosen by hand; these are not.  Widths, feed-forward sizes and
 vocabularies are any number (odd ones too: no vector load may assume a multiple of 8), head counts and groups
-are free, pages hold 1 to 64 tokens, some layers have a window.  Head sizes are those that other tests compile
-anyway, so that this file adds no compilation.  Each sequence is run whole, with its last 24 tokens decoded one by
+are free, pages hold 1 to 64 tokens, some layers have a window.  Head sizes are mostly those that other tests compile
+anyway; two are even numbers that are no multiple of 16 (40 and 72: the all-sizes kernels pad them).  Each sequence is run whole, with its last 24 tokens decoded one by
 one, and in portions; tolerances as in the replay tests.
 """
 import random
@@ -16,7 +16,7 @@ import plain_qwen3 as P
 
 pytestmark = pytest.mark.gpu
 
-HEAD_SIZES = [16, 32, 48, 64, 128]
+HEAD_SIZES = [16, 32, 48, 64, 128, 40, 72]
 TOL = {"float32": 1e-5, "bfloat16": 2.0 ** -5}
 T = 200
 PLANS = {"whole": [T], "last 24 decoded": [T - 24] + [1] * 24, "portions": [2, 17, 3, 64, 2, 9, 31, 5, 67]}
@@ -53,7 +53,7 @@ def run_plan(engine, ids, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("index", range(10))
+@pytest.mark.parametrize("index", range(14))
 def test_a_configuration_drawn_at_random(index, dtype, tmp_path):
     from llm_infer_rust_b200 import random_tensors, write_random_model
     from llm_infer_rust_b200.engine import Engine

@@ -128,13 +128,13 @@ def test_mixed_with_pages_used_again(name, dtype, tiny, tiny_weights, tiny_dirs,
 
 @pytest.mark.parametrize("name", ["B", "E"])
 def test_a_checkpoint_stored_in_32_bit_under_the_bfloat16_engine(name, tiny, tiny_weights, tiny_dirs, tmp_path):
-    """A tensor stored in 32-bit stays so: with a float32 folder the bfloat16 engine keeps every weight in float32
-    (the products widen the bfloat16 activations), and the logits are those of the float32 weights within the
-    bfloat16 engine's bound."""
+    """A checkpoint that is 32-bit as a whole is converted to the engine's dtype when it is bound (the reference:
+    src/models/qwen3/model.rs:616): the logits are those of the weights rounded to bfloat16, and the bfloat16
+    products (few-row kernels, tensor-core attention) run, not the 32-bit ones."""
     raw, page = tiny[name]["raw"], tiny[name]["page_size"]
     vocab, T = raw["vocab_size"], LENGTHS[name]
     ids = tokens(vocab, T, 12)
-    want = oracle(tiny_weights[name], raw, ids, "float32")
+    want = oracle(tiny_weights[name], raw, ids, "bfloat16")
     rp = Replay(tiny_dirs[name], "bfloat16", 2 * T, str(tmp_path / "out"), vocab, ["--page-size", str(page)])
     try:
         check(run_alone(rp, "whole", ids, [T]), want, "bfloat16", "whole")

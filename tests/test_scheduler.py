@@ -373,3 +373,32 @@ def test_random_traffic_keeps_every_promise(seed):
         elif why == rt.FinishReason.Length:
             assert len(got) == m or n + len(got) >= max_seq
             assert ignore or stop not in got
+
+
+def test_a_step_that_could_not_be_built_is_rolled_back():
+    """Nothing of the step ran: the requests that the plan admitted give back their promise and stand at the head
+    of the queue again in their old order; the running ones are untouched and the next plan is the same plan
+    (reference: src/scheduler/prefill.rs:65-71, :119-129)."""
+    cache, s = make(pages=32, budget=8)
+    a = s.add_request([1, 2, 3], params())
+    run_step(cache, s)                                         # a runs
+    b = s.add_request([4, 5], params())
+    c = s.add_request([6, 7, 8], params())
+    d = s.add_request([9] * 20, params())
+    free = cache.free_pages(0)
+    unpromised = cache.unpromised_pages(0)
+    plan = s.plan_step()
+    assert shape(plan) == [(a, 3, 1, True), (b, 0, 2, True), (c, 0, 3, True), (d, 0, 3, False)]
+    assert s.num_pending() == 0 and cache.unpromised_pages(0) < unpromised
+    assert s.rollback_step(plan) == 3
+    assert s.num_pending() == 3 and s.num_running() == 1 and cache.check() == ""
+    assert cache.free_pages(0) == free and cache.unpromised_pages(0) == unpromised
+    assert s.status_of(b) == rt.Status.Waiting and s.status_of(a) == rt.Status.Decoding
+    again = s.plan_step()
+    assert shape(again) == shape(plan)                         # arrival order is kept
+    assert s.rollback_step(again) == 3
+    plan, out = run_step(cache, s)
+    assert [o.uid for o in out] == [a, b, c]
+    # a request whose prompt is already partly through is not sent back
+    plan = s.plan_step()
+    assert (d, 3, 8, False) in shape(plan) and s.rollback_step(plan) == 0 and s.num_running() == 4

@@ -96,7 +96,7 @@ def register_toys():
         return ModelSpec(
             architecture="ToyHybridForCausalLM", vocab_size=c.vocab, hidden_size=c.hidden, max_positions=c.max_pos,
             embedding=PartSpec("token_embedding", {"vocab_size": c.vocab, "hidden_size": c.hidden}),
-            layers=(LayerSpec(block, attn, ffn, norm), LayerSpec(block, toy, ffn, norm)),
+            layers=(LayerSpec.pre_norm(block, attn, ffn, norm), LayerSpec.pre_norm(block, toy, ffn, norm)),
             run_list=(RunEntry(0), RunEntry(1), RunEntry(0, reads=0), RunEntry(1)),
             final_norm=norm, lm_head=PartSpec("linear_head", {"vocab_size": c.vocab, "hidden_size": c.hidden,
                                                               "tied": True}),
@@ -298,7 +298,7 @@ def register_routed_toys():
             architecture="ToyRoutedForCausalLM", vocab_size=c["vocab_size"], hidden_size=h,
             max_positions=c["max_position_embeddings"],
             embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": h}),
-            layers=(LayerSpec(block, attn, dense, norm), LayerSpec(block, attn, routed, norm)),
+            layers=(LayerSpec.pre_norm(block, attn, dense, norm), LayerSpec.pre_norm(block, attn, routed, norm)),
             run_list=(RunEntry(0), RunEntry(1)), final_norm=norm,
             lm_head=PartSpec("linear_head", {"vocab_size": c["vocab_size"], "hidden_size": h, "tied": False}),
             position_encodings={"scaled": PartSpec("toy_scaled_partial_rope", {

@@ -88,6 +88,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tiny, tmp_path):
     w["model.layers.7.mlp.up_proj.weight"] = torch.zeros(2, 2)
     w["extra.bias"] = torch.zeros(3)
     _rewrite(d, w)
+    # (tensors that the model does not know refuse nothing by themselves, but the one error lists them)
     with pytest.raises(WeightError) as info:
         _load(d)
     err = info.value
@@ -100,27 +101,101 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tiny, tmp_path):
         assert needle in text
 
 
+def test_unexpected_tensors_alone_are_ignored(tiny, tmp_path, caplog):
+    """A checkpoint with buffers beyond the model's tensors loads (the reference drops the leftover map:
+    src/models/qwen3/model.rs:223-265); their number is in the debug log."""
+    import logging
+    v = tiny["A"]
+    d = write_random_model(str(tmp_path), v["raw"], v["seed"])
+    w = random_tensors(v["raw"], v["seed"])
+    w["model.rotary_emb.inv_freq"] = torch.zeros(8)
+    w["extra.bias"] = torch.zeros(3)
+    _rewrite(d, w)
+    with caplog.at_level(logging.DEBUG, logger="llm_infer_rust_b200"):
+        model, loaded = _load(d)
+    assert not model.unbound_parameters() and "extra.bias" not in loaded
+    assert any("2 tensors that the model does not know are ignored" in r.getMessage() for r in caplog.records)
+
+
 def test_dtype_rule():
     bf, f32 = torch.bfloat16, torch.float32
     assert kept_dtype(torch.float16, bf) == bf and kept_dtype(bf, bf) == bf
-    assert kept_dtype(f32, bf) == f32                         # stored in 32-bit: stays so
+    assert kept_dtype(f32, bf) == bf                          # converted to the engine's dtype ...
+    assert kept_dtype(f32, bf, keep_float32=True) == f32      # ... unless the loader says that 32-bit tensors stay
     assert kept_dtype(bf, f32) == f32 and kept_dtype(f32, f32) == f32
     assert kept_dtype(torch.int64, bf) == torch.int32 and kept_dtype(torch.int32, f32) == torch.int32
 
 
-def test_a_tensor_stored_in_32_bit_stays_so_in_a_bfloat16_model(tiny, tmp_path):
+def _mixed_folder(tiny, tmp_path, declared):
     v = tiny["A"]
     w = {n: t.to(torch.bfloat16) for n, t in random_tensors(v["raw"], v["seed"]).items()}
     w["model.norm.weight"] = w["model.norm.weight"].float()
     w["model.layers.0.self_attn.q_norm.weight"] = w["model.layers.0.self_attn.q_norm.weight"].float()
     with open(tmp_path / "config.json", "w") as fh:
-        json.dump(v["raw"], fh)
+        json.dump(dict(v["raw"], torch_dtype=declared), fh)
     _rewrite(str(tmp_path), w)
-    model, _ = _load(str(tmp_path), torch.bfloat16)
+    return str(tmp_path)
+
+
+def test_a_tensor_stored_in_32_bit_in_a_16_bit_checkpoint_stays_so(tiny, tmp_path):
+    d = _mixed_folder(tiny, tmp_path, "bfloat16")
+    model, _ = _load(d, torch.bfloat16)
     assert model.parameter("final_norm.weight").dtype == torch.float32
     assert model.parameter("layers.0.mixer.q_norm").dtype == torch.float32
     assert model.parameter("layers.0.mixer.k_norm").dtype == torch.bfloat16
     assert model.parameter("layers.1.mixer.qkv_proj").dtype == torch.bfloat16
+
+
+def test_a_float32_checkpoint_becomes_bfloat16_under_a_bfloat16_engine(tiny, tmp_path, caplog):
+    """The reference converts every tensor to the engine's dtype when it binds it (src/models/qwen3/model.rs:616)."""
+    import logging
+    v = tiny["B"]
+    d = write_random_model(str(tmp_path), v["raw"], v["seed"])          # float32 folder, declared float32
+    with caplog.at_level(logging.INFO, logger="llm_infer_rust_b200"):
+        model, loaded = _load(d, torch.bfloat16)
+    shapes = model.parameter_shapes()
+    assert all(model.parameter(path).dtype == torch.bfloat16 for path in shapes)
+    assert any(f"{len(loaded)} tensors stored in 32-bit were converted to bfloat16" in r.getMessage() for r in caplog.records)
+    # the override keeps them, for whoever wants the 32-bit products
+    arch = resolve_architecture(v["raw"])
+    config = arch.parse_config(v["raw"])
+    wide = DecoderModel(arch.model_spec(config), torch.bfloat16, torch.device("cpu"))
+    load_weights(wide, arch.weight_plan(config), d, torch.bfloat16, torch.device("cpu"), keep_float32=True)
+    assert all(wide.parameter(path).dtype == torch.float32 for path in shapes)
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The generator of the random-weights mode, restated in NumPy from its description: two SplitMix64 words per
+    element, the sum of their eight 16-bit fields, centred and scaled.  Equal bit for bit, on any cut."""
+    import zlib
+    import numpy as np
+    from llm_infer_rust_b200.weights.random_init import counter_normal
+
+    def mix(x):
+        with np.errstate(over="ignore"):
+            x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+            x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return x ^ (x >> np.uint64(31))
+
+    def restated(seed, name, n):
+        with np.errstate(over="ignore"):
+            key = mix(mix(np.uint64(seed)) ^ (np.uint64(zlib.crc32(name.encode())) * np.uint64(0x9E3779B97F4A7C15)))
+            i = np.arange(n, dtype=np.uint64)
+            total = np.zeros(n, dtype=np.int64)
+            for word in (0, 1):
+                h = mix(key + i * np.uint64(2) + np.uint64(word))
+                for field in range(4):
+                    total += ((h >> np.uint64(16 * field)) & np.uint64(0xFFFF)).astype(np.int64)
+        scale = np.float32(1.0 / np.sqrt(8 * (65536.0 ** 2 - 1.0) / 12.0))
+        return (total.astype(np.float32) - np.float32(8 * 32767.5)) * scale
+
+    for seed, name, shape in ((0, "model.embed_tokens.weight", (7, 13)), (5, "model.layers.3.mlp.up_proj.weight", (1000,))):
+        got = counter_normal(seed, name, shape)
+        want = restated(seed, name, got.numel())
+        assert np.array_equal(got.view(-1).numpy(), want)
+    big = counter_normal(1, "x", (200000,))
+    assert abs(big.mean().item()) < 0.01 and abs(big.std().item() - 1.0) < 0.01
+    assert not torch.equal(counter_normal(1, "x", (64,)), counter_normal(1, "y", (64,)))
 
 
 def test_shards_duplicates_and_unsafe_paths(tiny, tmp_path):
