@@ -10,7 +10,11 @@
 // implicit device synchronisation is not acceptable.  For them this file keeps the
 // scratch inside the library itself, in a file-scope __device__ array.  Every GPU
 // on which the library is loaded holds that array (B200_STATIC_SCRATCH_FLOATS
-// floats, 4 MiB by default) from load until the process exits.
+// floats, 4 MiB by default) from load until the process exits.  The library is
+// compiled once per head size (-DHEAD_DIM): each of those libraries carries an
+// array of its own, so a process that loads three head sizes holds three arrays
+// per GPU, and "one array that all calls share" below means the calls of one
+// head size.
 //
 // What a caller has to know:
 //  * Nothing here calls cudaMalloc, cudaFree or any allocating routine; inputs and
@@ -20,6 +24,10 @@
 //    code the array's name is only a stand-in for the symbol, never a device
 //    pointer, so the kernels are always handed the looked-up address.  Make that
 //    first call per device before any stream capture starts.
+//  * The array that a call uses is the one of the CURRENT device (cudaGetDevice at
+//    the time of the call), not of the stream's or the pointers' device: make the
+//    device of `stream`, of the inputs and of the output current before calling.
+//    An output pointer that belongs to another device is refused (B200_BAD_SIZE).
 //  * A problem whose partials do not fit (n_rows * nh * splits * (head_dim + 2)
 //    floats) is refused with B200_STATIC_TOO_LARGE; nothing is launched.
 //  * All calls on a device share the one array, and it keeps whatever the last
@@ -81,6 +89,14 @@ B200_EXPORT int b200_decode_attention_static(const void* q, const void* k_cache,
   float* scratch = nullptr;
   const int rc = static_scratch(&scratch);
   if (rc != 0) return rc;
+  {
+    // the array belongs to the current device: an output that lives elsewhere would get the wrong device's array
+    int device = -1;
+    cudaPointerAttributes attr;
+    if (cudaGetDevice(&device) == cudaSuccess && cudaPointerGetAttributes(&attr, out) == cudaSuccess &&
+        attr.type == cudaMemoryTypeDevice && attr.device != device)
+      return B200_BAD_SIZE;
+  }
   float* part_acc = scratch;
   float* part_ml = scratch + static_cast<size_t>(n_rows) * nh * splits * D;
   if (dtype == B200_F32)

@@ -521,6 +521,7 @@ linear_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constan
         if (flags[1] != 0) { alive = false; break; }
       } else {
         // ---- the groups' sums are added in shared memory, group after group
+        consumer_sync();                                    // (the epilogue of the tile before has read `red`)
         for (int turn = 0; turn < GROUPS; ++turn) {
           if (grp == turn) {
 #pragma unroll

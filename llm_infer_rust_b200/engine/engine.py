@@ -224,6 +224,7 @@ class Engine:
         self.sampler = Sampler(self.device)
         self._meta = self._new_meta_buffers()
         self._scratch: Optional[torch.Tensor] = None
+        self._outgrown_scratch: List[torch.Tensor] = []
         self._params: Dict[int, SamplingParams] = {}
         self._seeds: Dict[int, int] = {}
         self.cpu_gpu_overlap = bool(cpu_gpu_overlap)
@@ -245,6 +246,12 @@ class Engine:
         self._shape_graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
         self._shape_seen: Dict[tuple, int] = {}
         self._shape_graph_limit = 6
+        # Decode graphs are captured now, while every page and state slot is free: a capture runs on throw-away
+        # requests (see _capture), and a full engine has no room for those.  A bucket for which even the empty
+        # pool is too small is tried again at its first use.
+        for bucket, g in sorted(self._graphs.items()):
+            if not self._capture(g, [1] * bucket, [1] * bucket, [0] * bucket):
+                log.debug("the decode graph of %d rows waits for free pages and state slots", bucket)
 
     # ------------------------------------------------------------------ the device
     def _setup_device(self, device: str) -> None:
@@ -284,6 +291,9 @@ class Engine:
         if self._scratch is None or self._scratch.numel() < floats:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("scratch memory must be sized before a graph is captured")
+            if self._scratch is not None:
+                # Graphs captured so far hold the address of the smaller buffer: it stays alive beside the new one.
+                self._outgrown_scratch.append(self._scratch)
             self._scratch = torch.empty(max(floats, 1 << 16), dtype=torch.float32, device=self.device)
         return self._scratch
 

@@ -390,15 +390,20 @@ def test_a_dropped_engine_in_a_dead_cycle_does_not_break_the_next_capture(tiny, 
         ring = [first]
         ring.append(ring)
         del first, ring                                       # unreachable; only the cycle collector can free it
-        second = engine(folder, cuda_graph_bs=2, **common)
-        forward, collected = second.model.forward, []
+        # (decode graphs are captured when an engine is built: the collector is made to run inside those captures)
+        from llm_infer_rust_b200.parts import DecoderModel
+        forward, collected = DecoderModel.forward, []
 
-        def collecting_forward(*args, **kwargs):
+        def collecting_forward(self, *args, **kwargs):
             if torch.cuda.is_current_stream_capturing():
                 collected.append(gc.collect())
-            return forward(*args, **kwargs)
+            return forward(self, *args, **kwargs)
 
-        second.model.forward = collecting_forward
+        DecoderModel.forward = collecting_forward
+        try:
+            second = engine(folder, cuda_graph_bs=2, **common)
+        finally:
+            DecoderModel.forward = forward
         assert [r.tokens for r in second.generate(prompts, params)] == want
         assert collected, "no decode graph was captured"
     finally:

@@ -495,7 +495,7 @@ def test_window_edge_is_exact():
 def test_refused_sizes_raise():
     o = ops()
     with pytest.raises(o.KernelError, match="head size"):
-        o._attention(24)
+        o._attention(25)                                          # odd: the rotation pairs dimensions
     with pytest.raises(o.KernelError, match="head size"):
         o._attention(528)
     with pytest.raises(o.KernelError, match="CUDA tensors"):

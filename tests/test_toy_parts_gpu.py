@@ -47,20 +47,22 @@ def register_toys():
             return StateSpec((self.n,), torch.float32)
 
         def forward(self, x, ctx, cache):
-            u = ops.linear(x, self.params["w_in"]).float()
-            lay, host = ctx.layout, ctx.host
-            cu = host[lay.off_cu_q: lay.off_cu_q + ctx.num_rows + 1]
-            prefix = host[lay.off_prefix_len: lay.off_prefix_len + ctx.num_rows]
-            slots = host[lay.off_state_slot: lay.off_state_slot + ctx.num_rows]
-            states = torch.empty_like(u)
-            for r in range(ctx.num_rows):
-                s = cache.state[int(slots[r])]
-                if prefix[r] == 0:
-                    s = torch.zeros_like(s)
-                for t in range(int(cu[r]), int(cu[r + 1])):
-                    s = self.decay * s + u[t]
-                    states[t] = s
-                cache.state[int(slots[r])] = s
+            """Works from the step's index arrays on the device alone (no number is read on the host), so the same
+            code runs eagerly and inside a captured graph, whose context has no host copy."""
+            u = ops.linear(x, self.params["w_in"]).float()                        # [T, n]
+            row = ctx.row_of_token.long()                                         # [T]
+            cu, slots = ctx.cu_q.long(), ctx.state_slots.long()
+            t = torch.arange(u.shape[0], device=u.device)
+            local = t - cu[row]                                                   # index of a token inside its row
+            before = cache.state[slots] * (ctx.prefix_len != 0).to(torch.float32)[:, None]   # fresh rows start from zeros
+            # s_t = decay^(i+1) s_before + sum over j <= t of the same row of decay^(t-j) u_j
+            ages = (t[:, None] - t[None, :]).to(torch.float32)
+            same = (row[:, None] == row[None, :]) & (t[None, :] <= t[:, None])
+            weights = torch.where(same, torch.pow(torch.full_like(ages, self.decay), ages.clamp_min(0.0)),
+                                  torch.zeros_like(ages))
+            states = weights @ u + torch.pow(torch.full_like(local, self.decay, dtype=torch.float32),
+                                             (local + 1).to(torch.float32))[:, None] * before[row]
+            cache.state.index_copy_(0, slots, states[cu[1:] - 1])                 # (padding rows write the sink slot 0)
             return ops.linear(states.to(x.dtype), self.params["w_out"])
 
     register_part("mixer", "toy_decay", DecayMixer, replace=True)
@@ -223,6 +225,38 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             scale = max(1.0, np.abs(want[r]).max())
             err = np.abs(got[r] - want[r]).max()
             assert err <= 1e-5 * scale, (name, r, err)
+
+
+def test_the_stateful_toy_mixer_inside_decode_graphs(tmp_path):
+    """bfloat16 with decode graphs on: a graph is captured on throw-away requests, so a live request's state
+    advances once per step, also in the step that uses a graph for the first time; a padded batch (3 rows in the
+    graph of 4) writes its padding row's state to the sink slot."""
+    register_toys()
+    from llm_infer_rust_b200 import random_tensors, write_random_model
+    from llm_infer_rust_b200.engine import Engine, StepEntry
+    d = write_random_model(str(tmp_path), RAW, seed=4, norm_std=0.1, dtype="bfloat16")
+    w = {n: t.to(torch.bfloat16) for n, t in random_tensors(RAW, 4, norm_std=0.1).items()}
+    eng = Engine(d, dtype="bfloat16", max_running_req=4, page_size=8, max_total_tokens=512, cuda_graph_bs=4)
+    assert all(g.graph is not None for g in eng._graphs.values())
+    g = torch.Generator().manual_seed(11)
+    seqs = {r: torch.randint(0, 211, (n,), generator=g).tolist() for r, n in ((1, 60), (2, 41), (3, 52))}
+    want = {r: plain_toy_forward(w, ids).numpy() for r, ids in seqs.items()}
+    decoded = 20
+    got = {r: [] for r in seqs}
+    for r, ids in seqs.items():
+        eng.open_request(r)
+        n = len(ids) - decoded
+        got[r].append(eng.step([StepEntry(r, ids[:n], list(range(n)))]).float().cpu().numpy())
+    for k in range(decoded):
+        live = [r for r in seqs if not (r == 2 and k >= 12)]        # 3 rows in the graph of 4, then 2 rows in the graph of 2
+        logits = eng.step([StepEntry(r, [seqs[r][len(seqs[r]) - decoded + k]], [0]) for r in live]).float().cpu().numpy()
+        for i, r in enumerate(live):
+            got[r].append(logits[i:i + 1])
+    eng.check_kernel_errors()
+    for r, ids in seqs.items():
+        rows = np.concatenate(got[r])
+        ref = want[r][:rows.shape[0]]
+        assert np.abs(rows - ref).max() <= 2.0 ** -5 * max(1.0, np.abs(ref).max()), r
 
 
 # ----------------------------------------------------------------------------- routed experts, another position encoding
