@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, with its share of the roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--shape 0.6b|8b|32b] [--layers L]
-                    [--batch B] [--context C] [--impl ours|reference]
+                    [--batch B] [--context C] [--point-shapes 8b,32b] [--no-points] [--impl ours|reference]
 
 A step is one decode step of a batch of B requests whose context ends at C tokens: the
 requests are prefilled with random token ids up to C - W - K tokens, W + K tokens are
@@ -18,7 +18,13 @@ decoded greedily, and the last K steps are timed.  One JSON line is printed:
 * ``prefill``: one step of 2,048 prompt tokens; ``frac`` = its FLOPs / time / the bfloat16 peak;
 * ``roofline``: bytes that a decode step must read (every weight once and the cache of the live
   requests) / its time, against the measured copy bandwidth;
-* ``points``: decoded tokens a second at batch 1 and 64, same context.
+* ``points``: decoded tokens a second at batch 1 and 64 at the same context and at the headline batch at half the
+  context, each with ``_frac``, its share of the roofline (bytes as above / time / measured copy bandwidth); then the
+  same figures (``<shape>_decode_b1`` ... ``<shape>_prefill_frac``) for the other shapes of ``--point-shapes``, by
+  default the Qwen3-8B and Qwen3-32B layer sizes with all their layers (each engine is built, measured with a quarter
+  of the steps and released before the next);
+* ``routing``: which products of a decode step ran on this package's few-row kernels and which on the library (a
+  rule of sizes, not a measurement: the same line again on the same machine takes the same kernels).
 
 Peaks come from MEASURED_PEAKS.json beside this file when it is there.  Weights are random
 (drawn on the device), token ids are synthetic.  One GPU only.
@@ -216,6 +222,71 @@ def prefill_timed(engine, T, vocab, repeats=3):
     return best
 
 
+def step_bytes(numbers, batch, mean_context):
+    """Bytes that a decode step has to read: every weight once and the cache of the live requests."""
+    return numbers["decode_weight_bytes"] + batch * mean_context * numbers["kv_bytes_per_token"]
+
+
+def routing_of(engine, rows):
+    """Which way the products of a step of `rows` tokens go: this package's few-row kernels or the library."""
+    from llm_infer_rust_b200.kernels import ops
+    block = engine.model.blocks[0]
+    mixer, ff = block.mixer, block.feed_forward
+    ways = {"qkv": ops.few_row_takes(rows, mixer.params["qkv_proj"], engine.dtype, ops.EPI_QKV, mixer.d),
+            "o": ops.few_row_takes(rows, mixer.params["o_proj"], engine.dtype),
+            "gate_up": ops.few_row_takes(rows, ff.params["gate_up_proj"], engine.dtype, ops.EPI_SWIGLU),
+            "down": ops.few_row_takes(rows, ff.params["down_proj"], engine.dtype),
+            "head": ops.few_row_takes(rows, engine.model.lm_head.params["weight"], engine.dtype, ops.EPI_PLAIN_F32)}
+    library = [name for name, kernel in ways.items() if not kernel]
+    return f"{ops.few_row_route} kernel" + (f", library for {'+'.join(library)}" if library else "")
+
+
+def build_engine(shape_name, layers, biggest, context):
+    from llm_infer_rust_b200.engine import Engine
+    shape = dict(SHAPES[shape_name])
+    full_layers = shape["num_hidden_layers"]
+    if layers:
+        shape["num_hidden_layers"] = min(layers, full_layers)
+    raw = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], rope_theta=1e6, rms_norm_eps=1e-6,
+               torch_dtype="bfloat16", eos_token_id=None, **shape)
+    pool_tokens = biggest * (context + 128) + 4096
+    engine = Engine(None, random_weights_config=raw, random_weights_seed=0, dtype="bfloat16",
+                    max_running_req=biggest, max_seq_len=context + 64, page_size=16,
+                    max_total_tokens=pool_tokens, cuda_graph_bs=biggest, chunked_prefill_size=4096,
+                    prefill_cuda_graph_max_tokens=2048, log_level="warn")
+    return engine, raw, full_layers
+
+
+def release():
+    """Give the memory of an engine that the caller has just dropped back to the device (the next engine sizes its
+    cache pool from what is free)."""
+    import gc
+    import torch
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+
+
+def measure_point_shape(shape_name, context, steps, warmup, peak):
+    """Decode at batch 1 / 8 / 64 and a prefill of 2,048 tokens at another shape, each with its share of the roofline."""
+    engine, raw, _ = build_engine(shape_name, None, 64, context)
+    numbers, vocab = model_numbers(raw), raw["vocab_size"]
+    out = {}
+    prefill_ms = prefill_timed(engine, 2048, vocab)
+    tag = shape_name.replace(".", "")
+    out[f"{tag}_prefill_tok_s"] = round(2048 * 1000.0 / prefill_ms, 1)
+    out[f"{tag}_prefill_frac"] = round(prefill_flops(raw, 2048) / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)
+    for b in (1, 8, 64):
+        run = decode_device_timed(engine, b, context, steps, warmup, vocab)
+        out[f"{tag}_decode_b{b}"] = round(run["tokens_per_s"], 1)
+        out[f"{tag}_decode_b{b}_frac"] = round(step_bytes(numbers, b, run["mean_context"]) / (run["ms_per_step"] * 1e-3) / 1e9
+                                               / peak["hbm_gbs"], 4)
+    routing = f"{shape_name}: {routing_of(engine, 8)}"
+    del engine
+    release()
+    return out, routing
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -226,7 +297,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the shape has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-points", action="store_true", help="only the headline shape at the headline batch")
+    ap.add_argument("--point-shapes", default="8b,32b",
+                    help="other shapes measured into `points` (decode at batch 1 / 8 / 64, prefill), comma separated")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase alone and print a short line (for profiling)")
     args = ap.parse_args()
@@ -238,23 +311,11 @@ def main() -> int:
         return 2
     args.warmup = max(args.warmup, 3)
 
-    import torch
-    from llm_infer_rust_b200.engine import Engine
-    shape = dict(SHAPES[args.shape])
-    full_layers = shape["num_hidden_layers"]
-    if args.layers:
-        shape["num_hidden_layers"] = min(args.layers, full_layers)
-    raw = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], rope_theta=1e6, rms_norm_eps=1e-6,
-               torch_dtype="bfloat16", eos_token_id=None, **shape)
+    biggest = args.batch if (args.no_points or args.only) else max(64, args.batch)
+    engine, raw, full_layers = build_engine(args.shape, args.layers, biggest, args.context)
     vocab = raw["vocab_size"]
     numbers = model_numbers(raw)
     peak, peak_source = peaks()
-    biggest = args.batch if (args.no_points or args.only) else max(64, args.batch)
-    pool_tokens = biggest * (args.context + 128) + 4096
-    engine = Engine(None, random_weights_config=raw, random_weights_seed=0, dtype="bfloat16",
-                    max_running_req=biggest, max_seq_len=args.context + 64, page_size=16,
-                    max_total_tokens=pool_tokens, cuda_graph_bs=biggest, chunked_prefill_size=4096,
-                    prefill_cuda_graph_max_tokens=2048)
 
     if args.only == "decode":
         run = decode_device_timed(engine, args.batch, args.context, args.steps, args.warmup, vocab)
@@ -267,18 +328,34 @@ def main() -> int:
     prefill_ms = prefill_timed(engine, 2048, vocab)
     flops = prefill_flops(raw, 2048)
     points = {}
+
+    def fraction(batch, run):
+        return round(step_bytes(numbers, batch, run["mean_context"]) / (run["ms_per_step"] * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
+
     if not args.no_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(decode_device_timed(engine, b, args.context, args.steps, args.warmup,
-                                                               vocab)["tokens_per_s"], 1)
+            run = decode_device_timed(engine, b, args.context, args.steps, args.warmup, vocab)
+            points[f"decode_b{b}"] = round(run["tokens_per_s"], 1)
+            points[f"decode_b{b}_frac"] = fraction(b, run)
+        # the same batch at half the context (the decode of a 2,048-token prompt starts there and ends at the headline's)
+        half = decode_device_timed(engine, args.batch, args.context // 2, args.steps, args.warmup, vocab)
+        points[f"decode_b{args.batch}_c{args.context // 2}"] = round(half["tokens_per_s"], 1)
+        points[f"decode_b{args.batch}_c{args.context // 2}_frac"] = fraction(args.batch, half)
     e2e = decode_end_to_end(engine, args.batch, args.context, args.steps, args.warmup, vocab)
     clocks = ClockSampler()
     clocks.start()
     main_run = decode_device_timed(engine, args.batch, args.context, args.steps, args.warmup, vocab)
     clock_record = clocks.stop()
+    routing = [f"{args.shape}: {routing_of(engine, args.batch)}"]
+    del engine
+    release()
+    if not args.no_points:
+        for name in [n for n in args.point_shapes.split(",") if n and n != args.shape]:
+            more, way = measure_point_shape(name, args.context, max(8, args.steps // 4), args.warmup, peak)
+            points.update(more)
+            routing.append(way)
 
-    step_bytes = numbers["decode_weight_bytes"] + args.batch * main_run["mean_context"] * numbers["kv_bytes_per_token"]
-    achieved = step_bytes / (main_run["ms_per_step"] * 1e-3) / 1e9
+    achieved = step_bytes(numbers, args.batch, main_run["mean_context"]) / (main_run["ms_per_step"] * 1e-3) / 1e9
     line = {
         "metric": "decode tokens/s", "value": round(main_run["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
@@ -302,6 +379,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": points,
+        "routing": "; ".join(routing),
     }
     print(json.dumps(line))
     return 0

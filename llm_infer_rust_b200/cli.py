@@ -14,37 +14,39 @@ import sys
 from typing import List, Optional
 
 USAGE = """Usage: python -m llm_infer_rust_b200 --model-path PATH [options]
-Options (as in the reference where it has them):
-  --model-path PATH         Model folder with config.json and model.safetensors
-  --memory-ratio R          GPU memory fraction for weights + KV cache (default 0.9)
-  --max-total-tokens N      Optional KV pool token cap (rounded down to whole pages)
-  --max-running-req N       Maximum active requests (default 256)
-  --max-prefill-tokens-per-batch N  Maximum uncached prefill tokens per batch (0 disables; default 8192)
-  --chunked-prefill-size N  Prefill token budget with long-request chunking (-1/0 disables; omitted auto-selects)
-  --cuda-graph-bs N         Maximum CUDA decode graph batch (0 disables; default max-running-req)
-  --prefill-cuda-graph-max-tokens N  Largest step with prompt tokens that is captured as a CUDA graph when its
-                            shape repeats (0 disables; default 2048)
-  --disable-cpu-gpu-overlap Read every step's tokens before the next step is put on the GPU (default: a step of
-                            decoded tokens is launched before the step before it has reported)
-  --max-seq-len N           Maximum sequence length (default 8192, at most the model's; must not exceed model config)
-  --page-size N             KV cache page size (default 16)
-  --dtype NAME              Model dtype: auto, bfloat16, float32
-  --device NAME             Device: auto or cuda (default auto)
-  --log-level LEVEL         trace/debug/info/warn/error (default info)
-  --tp-size N               Tensor parallel size (only 1 is supported)
-Accepted from the reference's command line and without effect here (there is no HTTP server, one attention
+Engine options (names and defaults follow the reference's command line):
+  --model-path PATH         folder that holds config.json and model.safetensors
+  --memory-ratio R          share of the GPU's memory that weights and cache together may take (0.9)
+  --max-total-tokens N      upper limit of the cache pool in tokens; whole pages only (none)
+  --max-running-req N       how many requests may be live at once (256)
+  --max-prefill-tokens-per-batch N  prompt tokens that one step may bring, 0 for no limit (8192)
+  --chunked-prefill-size N  prompts longer than this are cut into portions; -1 or 0 never cuts; left out,
+                            it is chosen from the GPU's memory
+  --cuda-graph-bs N         largest decode batch that replays a CUDA graph, 0 for none (max-running-req)
+  --prefill-cuda-graph-max-tokens N  steps with prompt tokens up to this size are captured as a graph when their
+                            shape comes again, 0 for none (2048)
+  --disable-cpu-gpu-overlap wait for every step's tokens before the next step goes to the GPU (by default a
+                            step of decoded tokens is launched while the one before still reports)
+  --max-seq-len N           longest sequence of a request, prompt and outputs; no more than the model's
+                            max_position_embeddings (8192)
+  --page-size N             tokens per cache page (16)
+  --dtype NAME              auto (the checkpoint's), bfloat16 or float32
+  --device NAME             auto or cuda; there is no CPU path (auto)
+  --log-level LEVEL         error, warn, info, debug or trace (info)
+  --tp-size N               must be 1: the engine runs on one GPU
+Read for the sake of launch scripts written for the reference, and without effect (no HTTP server, one attention
 backend, one way of uploading a step's index arrays):
   --host IP  --port PORT  --log-dir PATH  --trust-remote-code  --attention-backend fa|pt|flashinfer
   --enable-consecutive-prefill-overlap  --disable-async-metadata
 Prompts and sampling (token ids in, token ids out):
-  --prompt-ids IDS          Comma-separated token ids; may be given several times (else JSON lists on stdin)
+  --prompt-ids IDS          comma-separated token ids; may be given several times (else JSON lists on stdin)
   --temperature T  --top-k K  --top-p P  --max-tokens N  --ignore-eos  --seed S
 Random-weights mode (writes the model folder, then serves it if prompts are given):
-  --random-weights          Write config.json and model.safetensors into --model-path
+  --random-weights          write config.json and model.safetensors into --model-path
   --config PATH             config.json to build the random model from
-  --seed S                  Seed of the random weights (and of sampling)
+  --seed S                  seed of the random weights (and of sampling)
   --init-std X  --norm-std X   N(0, X) matrices (default 0.02); norm weights 1 + N(0, X) (default 0)
-  -h, --help                Show this help"""
+  -h, --help                this text"""
 
 
 # Options of the reference's server (src/server/cli.rs:13-36) that a launch script may carry over: they are read
