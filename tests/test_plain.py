@@ -142,3 +142,19 @@ def test_plain_generation_is_self_consistent(tiny, tiny_weights):
     seq = [5, 9, 17] + out
     logits = P.plain_forward(w, raw, seq[:-1])
     assert logits[2:].argmax(-1).tolist() == out
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_plain_implementation_has_not_drifted(name):
+    """Against the logits that tests/golden/make_golden.py recorded from this same implementation (see its header for
+    what that does and does not prove): same weights, same ids, same logits to float32 rounding."""
+    import os
+    import sys
+    import numpy as np
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, here)
+    import make_golden
+    stored = np.load(os.path.join(here, f"tiny_{name}.npz"))
+    ids, logits = make_golden.golden_case(name)
+    assert np.array_equal(ids, stored["ids"])
+    assert np.abs(logits - stored["logits"]).max() <= 1e-6 * max(1.0, float(np.abs(logits).max()))
