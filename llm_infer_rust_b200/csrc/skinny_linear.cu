@@ -476,18 +476,32 @@ static int choose_ksplit(int m, int n_tiles, int k, int sm_count) {
   const int kblocks = (k + BK - 1) / BK;
   const int need = (k + kc_max - 1) / kc_max;
   if (need > 8) return 0;
-  // Among the cluster sizes that leave every CTA at least sixteen k-blocks (128 KB of weights at 64 rows: below that
-  // the cluster's hand-over costs more than idle SMs), the one whose CTAs fill whole waves of the SMs best: 192
-  // tiles in clusters of 2 are 2.6 waves that run as long as 3, in clusters of 3 they are 3.9.  A larger cluster
-  // must win by a margin (its hand-over is longer).  Clusters of 3, 5, 6 or 7 are only taken while the grid stays
-  // under half the machine: measured at the Qwen3-8B sizes, 192 clusters of 3 ran 20 % longer than 192 clusters of 2
-  // (a cluster is placed on whole pairs of SMs, so an odd one leaves an SM idle), while 8 clusters of 3 beat 8 of 2.
+  // Clusters of 3, 5, 6 or 7 are only taken while the grid stays under half the machine: measured at the Qwen3-8B
+  // sizes, 192 clusters of 3 ran 20 % longer than 192 clusters of 2 (a cluster is placed on whole pairs of SMs, so an
+  // odd one leaves an SM idle), while 8 clusters of 3 beat 8 of 2.
+  auto allowed = [&](int split) {
+    return split == need || (split & (split - 1)) == 0 || 2ll * n_tiles * split <= sm_count;
+  };
+  // A grid that fits one wave of the SMs is bound by how fast ONE SM takes its share in, not by memory: as many CTAs
+  // as fit the wave, down to eight k-blocks (64 KB of weights at 64 rows) a CTA.  Measured at the Qwen3-0.6B sizes
+  // (decode, batch 8 / batch 1): 1.69 -> 1.56 ms and 1.16 -> 1.02 ms a step against a floor of sixteen k-blocks; a
+  // floor of four was slower again (1.66 ms): the cluster's hand-over then costs more than the SMs it wins.
+  int one_wave = 0;
+  for (int split = need; split <= 8; ++split) {
+    if (split > need && kblocks / split < 8) break;
+    if (static_cast<long long>(n_tiles) * split > sm_count) break;
+    if (allowed(split)) one_wave = split;
+  }
+  if (one_wave > 0) return one_wave;
+  // Several waves: every CTA pays its set-up again, so a CTA keeps at least sixteen k-blocks, and among those cluster
+  // sizes the one whose CTAs fill whole waves best wins (a larger cluster must win by a margin: its hand-over is
+  // longer).  At the Qwen3-8B sizes the floor of eight k-blocks made a step 7.7 ms instead of 5.0.
   int best = need;
   double best_fill = 0.0;
   for (int split = need; split <= 8; ++split) {
     if (split > need && kblocks / split < 16) break;
+    if (!allowed(split)) continue;
     const long long ctas = static_cast<long long>(n_tiles) * split;
-    if (split > need && (split & (split - 1)) != 0 && 2 * ctas > sm_count) continue;
     const long long waves = (ctas + sm_count - 1) / sm_count;
     const double fill = static_cast<double>(ctas) / static_cast<double>(waves * sm_count);
     if (fill > best_fill + 0.04) { best = split; best_fill = fill; }
