@@ -425,7 +425,16 @@ class _SkinnyParams(ctypes.Structure):
                 ("q_w", ctypes.c_void_p), ("k_w", ctypes.c_void_p), ("qk_w_f32", ctypes.c_int),
                 ("cos_table", ctypes.c_void_p), ("sin_table", ctypes.c_void_p), ("positions", ctypes.c_void_p),
                 ("slots", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
-                ("err", ctypes.c_void_p)]
+                ("err", ctypes.c_void_p), ("post_residual", ctypes.c_void_p), ("post_sum_out", ctypes.c_void_p),
+                ("post_stats", ctypes.c_void_p), ("stats_in", ctypes.c_void_p), ("stats_tiles", ctypes.c_int),
+                ("trace", ctypes.c_void_p)]
+
+
+# For tuning: an int64 tensor [4096, 32] on the device; the first thread of every CTA of the next single-product
+# launches then leaves the nanosecond clock there at the kernel's phases (0 start, 1 dependency wait over, 2 x staged,
+# 3 products done, 4 own sums stored, 5 the cluster's sums have met, 6 a rank other than 0 leaves, 7 epilogue done),
+# and in slots 16 to 31 the SM's cycle counter at the same places.
+skinny_trace: Optional[torch.Tensor] = None
 
 
 class PendingNorm:
@@ -466,7 +475,8 @@ def _sm_count(device) -> int:
 
 
 def _skinny():
-    lib = load_cuda_library("skinny_linear.cu")
+    # (with a trace buffer set, the build that stamps its clocks: a tuning aid, compiled when first asked for)
+    lib = load_cuda_library("skinny_linear.cu", {"SKINNY_TRACE": 1} if skinny_trace is not None else None)
     if not getattr(lib, "_checked", False):
         if lib.b200_skinny_params_size() != ctypes.sizeof(_SkinnyParams):
             raise KernelError("the parameter block of skinny_linear.cu and its Python mirror differ")
@@ -529,8 +539,15 @@ def graph_capture(graph: "torch.cuda.CUDAGraph"):
 
 
 def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
-                  qkv: Optional[dict] = None) -> torch.Tensor:
+                  qkv: Optional[dict] = None, out: Optional[torch.Tensor] = None, norm_after=None,
+                  stats=None) -> torch.Tensor:
     """epilogue(prologue(x) . weight^T) for at most 16 rows, in one kernel.
+
+    ``out``: the tensor to fill (PLAIN and SWIGLU; made here when None).  ``norm_after`` = (residual, sum_out,
+    stats): a PLAIN bfloat16 product also begins the add + RMSNorm that follows it: round(y + residual) goes to
+    ``sum_out`` and the sums of squares per tile of columns to ``stats`` (float32 [tiles, 16]).  ``stats`` =
+    (that tensor, tiles): a product whose ``x`` is a ``PendingNorm`` of such a y and residual takes the rows'
+    statistics from there and reads only its own columns (``residual_out`` is then not written: it is ``sum_out``).
 
     ``x``: a bfloat16 tensor [rows, K], or a ``PendingNorm`` (then the residual add and the norm run as the
     prologue and ``x.residual_out`` is filled).  ``mode``: EPI_PLAIN_BF16 / EPI_PLAIN_F32: the product;
@@ -538,6 +555,7 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     encoding and the cache store, with ``qkv`` = the keyword arguments of ``qkv_post`` (without ``qkv``);
     the result is then ``q_out``.
     """
+    _flush_held()
     if isinstance(x, PendingNorm) and x.residual is None:
         x = x.materialize()                                    # (this kernel's prologue always adds a residual)
     pending = x if isinstance(x, PendingNorm) else None
@@ -559,13 +577,16 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
         if pending.residual.dtype != torch.bfloat16 or pending.residual.shape != src.shape:
             raise KernelError("the residual must be bfloat16 and have the shape of x")
         P.residual = pending.residual.data_ptr()
-        P.residual_out = 0 if pending.residual_out is None else pending.residual_out.data_ptr()
+        P.residual_out = 0 if pending.residual_out is None or stats is not None else pending.residual_out.data_ptr()
+        if stats is not None:
+            P.stats_in, P.stats_tiles = stats[0].data_ptr(), int(stats[1])
         P.norm_w, P.norm_w_f32, P.eps = pending.weight.data_ptr(), int(pending.weight.dtype == torch.float32), pending.eps
         if pending.weight.numel() != k or pending.weight.dtype not in (torch.float32, torch.bfloat16):
             raise KernelError("the norm weight must have K elements, bfloat16 or float32")
     P.M, P.N, P.K, P.mode = m, n, k, mode
     dev = src.device
     P.err = error_word(dev).data_ptr()
+    P.trace = 0 if skinny_trace is None else skinny_trace.data_ptr()
     if mode == EPI_QKV:
         nh, nkv = qkv["num_heads"], qkv["num_kv_heads"]
         out = qkv["q_out"]
@@ -591,16 +612,74 @@ def skinny_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
         P.positions = qkv["positions"].data_ptr()
         P.slots = 0 if slots is None else slots.data_ptr()
         P.k_cache, P.v_cache = (0 if kc is None else kc.data_ptr()), (0 if vc is None else vc.data_ptr())
-    elif mode == EPI_SWIGLU:
-        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=dev)
-    else:
-        out = torch.empty((m, n), dtype=torch.float32 if mode == EPI_PLAIN_F32 else torch.bfloat16, device=dev)
+    elif out is None:
+        out = _few_row_out(m, n, mode, dev)
+    if norm_after is not None:
+        P.post_residual, P.post_sum_out, P.post_stats = (t.data_ptr() for t in norm_after)
     P.out = out.data_ptr()
     sms = _sm_count(dev)
     box = lib.b200_skinny_box_rows(mode, head_dim, n, sms)
     rc = lib.b200_skinny_linear(_weight_map(weight, box), ctypes.byref(P), head_dim, sms, _stream())
     _ok(rc, "skinny_linear")
     return out
+
+
+def _few_row_out(m: int, n: int, mode: int, device) -> torch.Tensor:
+    if mode == EPI_SWIGLU:
+        return torch.empty((m, n // 2), dtype=torch.bfloat16, device=device)
+    return torch.empty((m, n), dtype=torch.float32 if mode == EPI_PLAIN_F32 else torch.bfloat16, device=device)
+
+
+# A lazy PLAIN bfloat16 product of the "single" route is held back until the next launch is known: if that is a
+# product behind an add + RMSNorm of this product's result, the held product's epilogue begins the norm (the rounded
+# sum and the rows' sums of squares), and the next product reads only its own columns instead of whole rows, which
+# every one of its CTAs would otherwise fetch (at 4,096 columns that read took 5 of a product's 20 us).
+class _Held:
+    def __init__(self, x, weight, x_rows, out):
+        self.x, self.weight, self.x_rows, self.out = x, weight, x_rows, out
+
+
+_held: Optional[_Held] = None
+
+
+def _flush_held(norm_after=None) -> None:
+    """Launch the product that is held back (with the norm that follows it begun in its epilogue, if given)."""
+    global _held
+    h = _held
+    if h is None:
+        return
+    _held = None
+    skinny_linear(h.x, h.weight, EPI_PLAIN_BF16, x_rows=h.x_rows, out=h.out, norm_after=norm_after)
+
+
+def _single_lazy(x, weight, mode, x_rows, qkv, lazy) -> torch.Tensor:
+    """The "single" route of ``few_row_linear``."""
+    global _held
+    pending = x if isinstance(x, PendingNorm) else None
+    h = _held
+    stats = None
+    if (h is not None and pending is not None and pending.x is h.out and pending.residual is not None
+            and x_rows is None and pending.residual.dtype == torch.bfloat16
+            and pending.residual.shape == h.out.shape and pending.residual.is_contiguous()):
+        lib = _skinny()
+        sms = _sm_count(h.out.device)
+        n = h.weight.shape[0]
+        bn = lib.b200_skinny_tile_rows(EPI_PLAIN_BF16, 0, n, sms)
+        if bn <= 128:
+            tiles = -(-n // bn)
+            stat_t = torch.empty((tiles, SKINNY_MAX_ROWS), dtype=torch.float32, device=h.out.device)
+            sum_out = pending.residual_out if pending.residual_out is not None else torch.empty_like(pending.residual)
+            _flush_held((pending.residual, sum_out, stat_t))
+            stats = (stat_t, tiles)
+    _flush_held()
+    src = pending.x if pending is not None else x
+    rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
+    m = src.shape[0] if rows_t is None else rows_t.numel()
+    if (lazy and mode == EPI_PLAIN_BF16 and stats is None and (pending is None or pending.residual is not None)
+            and src.is_cuda and skinny_ok(m, weight, src.dtype, mode)):
+        _held = _Held(x, weight, x_rows, _few_row_out(m, weight.shape[0], mode, src.device))
+        return _held.out
+    return skinny_linear(x, weight, mode, x_rows=x_rows, qkv=qkv, stats=stats)
 
 
 # --------------------------------------------------------------------------- chains of few-row products
@@ -610,7 +689,7 @@ PRO_NONE, PRO_ADD_NORM, PRO_NORM = 0, 1, 2
 # "chain" (one persistent kernel for consecutive products, up to 64 rows: csrc/linear_chain.cu) or "library" (cuBLAS
 # with the norm, rotation and activation as kernels of their own).  Fixed by the environment or by assignment,
 # never by a measurement, so that two processes given the same input run the same kernels.  Measured on B200
-# (decode, batch 8, context 4,096): "single" 1.73 ms a step at the Qwen3-0.6B sizes and 5.0 ms at the 8B sizes,
+# (decode, batch 8, context 4,096): "single" 1.42 ms a step at the Qwen3-0.6B sizes and 4.4 ms at the 8B sizes,
 # "chain" 1.86 ms and 6.2 ms (its barriers and tile hand-overs cost what the launches did), so "single" is the default.
 few_row_route = os.environ.get("LLM_INFER_B200_FEW_ROW", "single")
 single_max_bytes = int(os.environ.get("LLM_INFER_B200_SINGLE_MAX_BYTES", 224 << 20))
@@ -753,7 +832,7 @@ def few_row_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: 
         if not lazy:
             flush_chain()
         return out
-    return skinny_linear(x, weight, mode, x_rows=x_rows, qkv=qkv)
+    return _single_lazy(x, weight, mode, x_rows, qkv, lazy)
 
 
 def _chain_append(pending, src, rows_t, m, weight, mode, qkv) -> torch.Tensor:
@@ -850,6 +929,7 @@ def chain_pending() -> int:
 def flush_chain() -> None:
     """Launch the products that wait in the chain (at most six per launch of the persistent kernel)."""
     global _chain
+    _flush_held()
     ch = _chain
     if ch is None:
         return

@@ -225,6 +225,79 @@ def test_few_row_product_qkv(m, nh, nkv, d, k, with_norm):
     o.check_errors(torch.device(DEV))
 
 
+@pytest.mark.parametrize("m,k0,hidden,n2,kind", [(1, 64, 128, 192, "plain"), (8, 2048, 1024, 6144, "swiglu"),
+                                                 (5, 96, 200, 130, "plain"), (16, 3072, 1000, 256, "swiglu"),
+                                                 (9, 512, 4096, 2 * 128 + 2 * 2 * 128, "qkv"), (3, 64, 72, 152001, "head")])
+def test_few_row_products_hand_the_norm_between_them_from_one_to_the_next(m, k0, hidden, n2, kind):
+    """A lazy product followed by a product behind the add + norm of its result: the first leaves the rounded sum
+    and the rows' sums of squares (per tile of its columns), the second reads only its own columns.  Compared with
+    the plain formula and with the same two products run one by one (where every CTA reads whole rows)."""
+    o = ops()
+    assert o.few_row_route == "single"
+    a, w1 = rnd(m, k0, dtype=torch.bfloat16), rnd(hidden, k0, dtype=torch.bfloat16, seed=1, scale=0.05)
+    res = rnd(m, hidden, dtype=torch.bfloat16, seed=2)
+    nw = (1 + 0.1 * rnd(hidden, seed=3)).to(torch.bfloat16)
+    w2 = rnd(n2, hidden, dtype=torch.bfloat16, seed=4, scale=0.05)
+    rows = torch.tensor([(2 * i + 1) % m for i in range(m)], dtype=torch.int32, device=DEV) if kind == "head" else None
+
+    def second(src):
+        if kind == "plain":
+            return o.few_row_linear(src, w2, o.EPI_PLAIN_BF16)
+        if kind == "head":
+            return o.few_row_linear(src, w2, o.EPI_PLAIN_F32)
+        if kind == "swiglu":
+            return o.few_row_linear(src, w2, o.EPI_SWIGLU)
+        q = torch.empty(m, 2 * 128, dtype=torch.bfloat16, device=DEV)
+        return o.few_row_linear(src, w2, o.EPI_QKV, qkv=dict(head_dim=128, num_heads=2, num_kv_heads=2, q_out=q,
+                                                             k_cache=None, v_cache=None, q_weight=None, k_weight=None,
+                                                             eps=1e-6, cos=None, sin=None, rot_dim=0,
+                                                             positions=torch.zeros(m, dtype=torch.int32, device=DEV),
+                                                             slots=None)).clone()
+
+    results = []
+    for lazy in (True, False):
+        y = o.few_row_linear(a, w1, o.EPI_PLAIN_BF16, lazy=lazy)
+        assert (o._held is not None) == lazy
+        src = o.PendingNorm(y, res, nw, 1e-5, rows=rows, write_residual=rows is None)
+        out = second(src)
+        assert o._held is None
+        results.append((y.clone(), None if rows is not None else src.residual_out.clone(), out.clone()))
+    (y1, sum1, out1), (y2, sum2, out2) = results
+    assert torch.equal(y1, y2)
+    y_want = a.float() @ w1.float().t()
+    assert (y1.float() - y_want).abs().max() <= 2.0 ** -7 * max(1.0, float(y_want.abs().max()))
+    s_sum = y1.float() + res.float()
+    if rows is None:
+        assert torch.equal(sum1, s_sum.to(torch.bfloat16)) and torch.equal(sum2, sum1)
+    sel = rows.long() if rows is not None else torch.arange(m, device=DEV)
+    xin = _bf(s_sum[sel] * nw.float())
+    want = (xin @ w2.float().t()) * torch.rsqrt((s_sum[sel] * s_sum[sel]).mean(-1, keepdim=True) + 1e-5)
+    if kind == "swiglu":
+        want = R.ref_silu_mul(_bf(want).to(torch.bfloat16)).float()
+    elif kind == "qkv":
+        want = want[:, :2 * 128]
+    scale = max(1.0, float(want.abs().max()))
+    for got in (out1, out2):
+        assert (got.float() - want).abs().max() <= 2.0 ** -6 * scale
+    assert (out1.float() - out2.float()).abs().max() <= 2.0 ** -7 * scale
+    o.check_errors(torch.device(DEV))
+
+
+def test_a_held_product_is_launched_before_anything_else_runs():
+    o = ops()
+    a, w = rnd(4, 256, dtype=torch.bfloat16), rnd(384, 256, dtype=torch.bfloat16, seed=1, scale=0.05)
+    y = o.few_row_linear(a, w, o.EPI_PLAIN_BF16, lazy=True)
+    assert o._held is not None
+    z = o.rms_norm(y, torch.ones(384, dtype=torch.bfloat16, device=DEV), 1e-6)       # any other wrapper launches it first
+    assert o._held is None
+    want = a.float() @ w.float().t()
+    assert (y.float() - want).abs().max() <= 2.0 ** -7 * max(1.0, float(want.abs().max()))
+    assert torch.isfinite(z.float()).all()
+    y2 = o.few_row_linear(a, w, o.EPI_PLAIN_BF16, lazy=True)
+    o.flush_chain()
+    assert o._held is None and torch.equal(y, y2)
+
+
 def test_few_row_product_refusals():
     o = ops()
     w = rnd(64, 64, dtype=torch.bfloat16)
