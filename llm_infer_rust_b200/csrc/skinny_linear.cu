@@ -169,13 +169,13 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
 template <int MT, int GROUPS>
 __device__ __forceinline__ float4 own_sums(const unsigned char* ring, int m, int n) {
   constexpr int WN = 16 * MT, STAGE_FLOATS = 64 * MT * 128 / 4;
-  const float* part = reinterpret_cast<const float*>(ring + (n / WN) * (WN * 128)) + m * (WN + 1) + n % WN;
-  float4 sum = make_float4(part[0], part[1], part[2], part[3]);
+  const float* part = reinterpret_cast<const float*>(ring + (n / WN) * (WN * 128)) + m * (WN + 4) + n % WN;
+  float4 more[GROUPS];
 #pragma unroll
-  for (int gg = 1; gg < GROUPS; ++gg) {
-    const float* more = part + gg * STAGE_FLOATS;
-    sum.x += more[0]; sum.y += more[1]; sum.z += more[2]; sum.w += more[3];
-  }
+  for (int gg = 0; gg < GROUPS; ++gg) more[gg] = *reinterpret_cast<const float4*>(part + gg * STAGE_FLOATS);
+  float4 sum = more[0];
+#pragma unroll
+  for (int gg = 1; gg < GROUPS; ++gg) { sum.x += more[gg].x; sum.y += more[gg].y; sum.z += more[gg].z; sum.w += more[gg].w; }
   return sum;
 }
 
@@ -484,6 +484,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
       if (!mbar_wait(full + s, (it / STAGES) & 1, p.err)) { ok = false; break; }
       const unsigned char* wt = ring + s * STAGE_BYTES;
       // All fragments of (half) a k-block are fetched before the first multiply, so that the fetches' latencies overlap.
+      // (Measured: one k-step at a time, rolled or unrolled, makes no difference to a decode step.)
       constexpr int KS = MT == 4 ? 2 : 4;
 #pragma unroll
       for (int ks0 = 0; ks0 < BK / 16; ks0 += KS) {
@@ -522,15 +523,17 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   constexpr int WN = 16 * MT;                      // weight rows of a warp
   const int g = lane >> 2, t2 = (lane & 3) * 2;
   if (!feeder) {
-    float* part = reinterpret_cast<float*>(ring + grp * STAGE_BYTES + rw * (WN * 128));      // [mpad][WN + 1]
+    // [mpad][WN + 4]: rows in 16-byte steps, and the four lanes of a quad (rows 2t, 2t + 1) fall on different banks
+    float* part = reinterpret_cast<float*>(ring + grp * STAGE_BYTES + rw * (WN * 128));
+    static_assert(MMAX * (WN + 4) * 4 <= WN * 128, "a warp's sums fit where its weight rows lay");
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const int m = nt * 8 + t2;
         if (m < mpad) {
-          float* r0 = part + m * (WN + 1) + i * 16 + g;
-          float* r1 = r0 + (WN + 1);
+          float* r0 = part + m * (WN + 4) + i * 16 + g;
+          float* r1 = r0 + (WN + 4);
           r0[0] = acc[i][nt][0]; r1[0] = acc[i][nt][1]; r0[8] = acc[i][nt][2]; r1[8] = acc[i][nt][3];
         }
       }
