@@ -573,20 +573,29 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
   }
   {
     const float* theirs[8];
+    if (pull) {
 #pragma unroll
-    for (int r = 1; r < 8; ++r)
-      theirs[r] = r >= p.ksplit ? red : pull ? cluster.map_shared_rank(red, r) : slots + (r - 1) * M * BN;
-    const int their_stride = pull ? RS : BN;
+      for (int r = 1; r < 8; ++r) theirs[r] = r < p.ksplit ? cluster.map_shared_rank(red, r) : red;
+    }
 #pragma unroll 1
     for (int i = threadIdx.x; i < M * QUADS; i += THREADS) {
       const int m = i / QUADS, n = (i - m * QUADS) * 4;
-      float4 part[8];                                // every rank's part is fetched before any is used
-#pragma unroll
-      for (int r = 1; r < 8; ++r)
-        part[r] = r < p.ksplit ? *reinterpret_cast<const float4*>(theirs[r] + m * their_stride + n) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       float4 sum = own_sums<MT, GROUPS>(ring, m, n);
+      if (push) {                                    // (this CTA's own shared memory: a short loop)
+        const float* theirs0 = slots + m * BN + n;
+#pragma unroll 1
+        for (int r = 1; r < p.ksplit; ++r, theirs0 += M * BN) {
+          const float4 part = *reinterpret_cast<const float4*>(theirs0);
+          sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
+        }
+      } else if (pull) {
+        float4 part[8];                              // every rank's part is fetched before any is used
 #pragma unroll
-      for (int r = 1; r < 8; ++r) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
+        for (int r = 1; r < 8; ++r)
+          part[r] = r < p.ksplit ? *reinterpret_cast<const float4*>(theirs[r] + m * RS + n) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int r = 1; r < 8; ++r) { sum.x += part[r].x; sum.y += part[r].y; sum.z += part[r].z; sum.w += part[r].w; }
+      }
       if (has_norm) { const float f = row_scale[m]; sum.x *= f; sum.y *= f; sum.z *= f; sum.w *= f; }
       if (p.mode == EPI_QKV || p.mode == EPI_SWIGLU) {
         // these products' outputs are bfloat16 tensors in the unfused path; the same rounding here
@@ -627,8 +636,13 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
             // The norm that follows: s = round(y) + residual in float (what its prologue would add up), stored
             // rounded, and the squares of s over this tile's columns.
 #pragma unroll
+            __align__(8) bf16 res[4];
+            if (whole) *reinterpret_cast<uint2*>(res) = *reinterpret_cast<const uint2*>(p.post_residual + at);
+            else
+              for (int e = 0; e < 4; ++e) res[e] = col + e < p.N ? p.post_residual[at + e] : __float2bfloat16_rn(0.0f);
+#pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float sum = col + e < p.N ? __bfloat162float(h[e]) + __bfloat162float(p.post_residual[at + e]) : 0.0f;
+              const float sum = col + e < p.N ? __bfloat162float(h[e]) + __bfloat162float(res[e]) : 0.0f;
               sums[e] = __float2bfloat16_rn(sum);
               ss += sum * sum;
             }
