@@ -157,6 +157,8 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&out)[8]) {
   }
 }
 
+template <int N> struct Count { static constexpr int value = N; };
+
 __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
   __align__(16) bf16 h[8];
 #pragma unroll
@@ -407,40 +409,47 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
     }
     const int chunks = kc / 8, total = M * chunks;
     const unsigned inverse = 0xffffffffu / static_cast<unsigned>(chunks) + 1u;   // c / chunks = umulhi(c, inverse) for these small c
+    // U chunks of 16 bytes a thread at a time: one where that covers everything (the usual case in a decode step:
+    // less code to run through), else four.
+    auto stage = [&](auto batch) {
+      constexpr int U = decltype(batch)::value;
 #pragma unroll 1
-    for (int base = 0; base < total; base += 4 * THREADS) {
-      uint4 xa[4], xb[4];
-      int at[4], kk[4];
+      for (int base = 0; base < total; base += U * THREADS) {
+        uint4 xa[U], xb[U];
+        int at[U], kk[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = base + u * THREADS + threadIdx.x;
-        const int m = static_cast<int>(__umulhi(static_cast<unsigned>(c), inverse)), j = (c - m * chunks) * 8;
-        at[u] = c < total ? m * ldx + j : -1;
-        kk[u] = c < total && k_lo + j < K ? j : -1;
-        xa[u] = xb[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (kk[u] >= 0) {
-          const size_t src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K + k_lo + j;
-          xa[u] = *reinterpret_cast<const uint4*>(p.x + src);
-          if (has_stats) xb[u] = *reinterpret_cast<const uint4*>(p.residual + src);
+        for (int u = 0; u < U; ++u) {
+          const int c = base + u * THREADS + threadIdx.x;
+          const int m = static_cast<int>(__umulhi(static_cast<unsigned>(c), inverse)), j = (c - m * chunks) * 8;
+          at[u] = c < total ? m * ldx + j : -1;
+          kk[u] = c < total && k_lo + j < K ? j : -1;
+          xa[u] = xb[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (kk[u] >= 0) {
+            const size_t src = static_cast<size_t>(p.x_rows ? p.x_rows[m] : m) * K + k_lo + j;
+            xa[u] = *reinterpret_cast<const uint4*>(p.x + src);
+            if (has_stats) xb[u] = *reinterpret_cast<const uint4*>(p.residual + src);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (at[u] < 0) continue;
+          if (has_stats && kk[u] >= 0) {
+            float sum[8], other[8];
+            unpack_bf16x8(xa[u], sum);
+            unpack_bf16x8(xb[u], other);
+            const float4 w0 = *reinterpret_cast<const float4*>(ws + kk[u]), w1 = *reinterpret_cast<const float4*>(ws + kk[u] + 4);
+            sum[0] = (sum[0] + other[0]) * w0.x; sum[1] = (sum[1] + other[1]) * w0.y;
+            sum[2] = (sum[2] + other[2]) * w0.z; sum[3] = (sum[3] + other[3]) * w0.w;
+            sum[4] = (sum[4] + other[4]) * w1.x; sum[5] = (sum[5] + other[5]) * w1.y;
+            sum[6] = (sum[6] + other[6]) * w1.z; sum[7] = (sum[7] + other[7]) * w1.w;
+            xa[u] = pack_bf16x8(sum);
+          }
+          *reinterpret_cast<uint4*>(xs + at[u]) = xa[u];
         }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (at[u] < 0) continue;
-        if (has_stats && kk[u] >= 0) {
-          float sum[8], other[8];
-          unpack_bf16x8(xa[u], sum);
-          unpack_bf16x8(xb[u], other);
-          const float4 w0 = *reinterpret_cast<const float4*>(ws + kk[u]), w1 = *reinterpret_cast<const float4*>(ws + kk[u] + 4);
-          sum[0] = (sum[0] + other[0]) * w0.x; sum[1] = (sum[1] + other[1]) * w0.y;
-          sum[2] = (sum[2] + other[2]) * w0.z; sum[3] = (sum[3] + other[3]) * w0.w;
-          sum[4] = (sum[4] + other[4]) * w1.x; sum[5] = (sum[5] + other[5]) * w1.y;
-          sum[6] = (sum[6] + other[6]) * w1.z; sum[7] = (sum[7] + other[7]) * w1.w;
-          xa[u] = pack_bf16x8(sum);
-        }
-        *reinterpret_cast<uint4*>(xs + at[u]) = xa[u];
-      }
-    }
+    };
+    if (total <= THREADS) stage(Count<1>());
+    else stage(Count<4>());
     if (has_stats) {
 #pragma unroll
       for (int rr = 0; rr < ROWS_PER_WARP; ++rr) {
@@ -635,7 +644,6 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap wmap, const SkinnyParam
           if (post) {
             // The norm that follows: s = round(y) + residual in float (what its prologue would add up), stored
             // rounded, and the squares of s over this tile's columns.
-#pragma unroll
             __align__(8) bf16 res[4];
             if (whole) *reinterpret_cast<uint2*>(res) = *reinterpret_cast<const uint2*>(p.post_residual + at);
             else
