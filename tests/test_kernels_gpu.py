@@ -135,7 +135,8 @@ def _bf(t):
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (5, 509, 96), (8, 1000, 1024), (13, 130, 3000), (16, 256, 2048),
                                    (3, 96, 12288), (16, 64, 12288), (2, 4000, 40),
-                                   (8, 152001, 64)])          # (a vocabulary: tiles of 256 weight rows)
+                                   (8, 152001, 64),           # (a vocabulary: tiles of 256 weight rows)
+                                   (5, 20000, 1088), (12, 19000, 2112)])   # (several waves of tiles: two CTAs an SM)
 @pytest.mark.parametrize("with_norm", [False, True])
 def test_few_row_product_plain(m, n, k, with_norm):
     """x . W^T for at most 16 rows, alone and with the residual add + norm as its prologue, in both output dtypes,
@@ -169,7 +170,8 @@ def test_few_row_product_plain(m, n, k, with_norm):
     o.check_errors(torch.device(DEV))
 
 
-@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 224, 96), (16, 3072, 1024), (4, 100, 4096)])
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 224, 96), (16, 3072, 1024), (4, 100, 4096),
+                                       (6, 10100, 1088)])     # (several waves of tiles: two CTAs an SM)
 def test_few_row_product_swiglu(m, inter, k):
     o = ops()
     x, w = rnd(m, k, dtype=torch.bfloat16), rnd(2 * inter, k, dtype=torch.bfloat16, seed=1, scale=0.1)
@@ -181,7 +183,8 @@ def test_few_row_product_swiglu(m, inter, k):
 
 
 @pytest.mark.parametrize("m,nh,nkv,d,k,with_norm", [(1, 4, 2, 64, 128, True), (9, 16, 8, 128, 1024, True),
-                                                    (16, 3, 1, 64, 200, False), (5, 2, 2, 256, 512, True)])
+                                                    (16, 3, 1, 64, 200, False), (5, 2, 2, 256, 512, True),
+                                                    (3, 150, 2, 128, 1088, True)])       # (154 heads: several waves)
 def test_few_row_product_qkv(m, nh, nkv, d, k, with_norm):
     """The fused QKV step against the separate kernels' references: projection, per-head norm, rotation, store."""
     o = ops()
