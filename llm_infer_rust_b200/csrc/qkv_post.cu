@@ -112,10 +112,22 @@ qkv_post_vec_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out, TA* __re
   const int t = live ? static_cast<int>(work / heads) : 0;
   const int h = live ? static_cast<int>(work - static_cast<long long>(t) * heads) : 0;
   const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+  // The token's position is fetched first, and the angles as soon as it is known: they depend on nothing else, and
+  // fetched where they are used they stood as two more round trips behind the head's values.
+  const bool turns = cos_table != nullptr && (is_q || is_k) && live;
+  const int pos = turns ? positions[t] : 0;
   float v[N];
 #pragma unroll
   for (int e = 0; e < N; ++e) v[e] = 0.0f;
   if (live) Vec16<TA>::load(qkv + (static_cast<size_t>(t) * heads + h) * d + sub * N, v);
+  const bool in_table = turns && pos >= 0 && pos < max_pos;
+  const bool first = sub < (lanes >> 1);
+  float c[N], sn[N];                                          // (one wide load each: a lane's N angles are contiguous)
+  if (in_table) {
+    const int ci = (first ? sub : sub - (lanes >> 1)) * N;
+    load_floats<float, N>(cos_table + static_cast<size_t>(pos) * (d / 2) + ci, c);
+    load_floats<float, N>(sin_table + static_cast<size_t>(pos) * (d / 2) + ci, sn);
+  }
 
   TA* dst = nullptr;
   if (live) {
@@ -151,16 +163,10 @@ qkv_post_vec_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out, TA* __re
   float partner[N];
 #pragma unroll
   for (int e = 0; e < N; ++e) partner[e] = __shfl_xor_sync(full, v[e], half_lanes, lanes);
-  if (cos_table != nullptr && (is_q || is_k) && live) {
-    const int pos = positions[t];
-    if (pos < 0 || pos >= max_pos) {
+  if (turns) {
+    if (!in_table) {
       if (sub == 0) atomicOr(err, B200_ERR_POSITION_RANGE);
     } else {
-      const bool first = sub < half_lanes;
-      const int ci = (first ? sub : sub - half_lanes) * N;
-      float c[N], sn[N];                                      // (one wide load each: a lane's N angles are contiguous)
-      load_floats<float, N>(cos_table + static_cast<size_t>(pos) * (d / 2) + ci, c);
-      load_floats<float, N>(sin_table + static_cast<size_t>(pos) * (d / 2) + ci, sn);
 #pragma unroll
       for (int e = 0; e < N; ++e) v[e] = first ? v[e] * c[e] - partner[e] * sn[e] : v[e] * c[e] + partner[e] * sn[e];
     }
