@@ -228,17 +228,19 @@ def step_bytes(numbers, batch, mean_context):
 
 
 def routing_of(engine, rows):
-    """Which way the products of a step of `rows` tokens go: this package's few-row kernels or the library."""
+    """Which way the products of a step of `rows` tokens go: this package's few-row kernels (the ring kernel, or the
+    streaming kernel for the largest weights) or the library."""
     from llm_infer_rust_b200.kernels import ops
     block = engine.model.blocks[0]
     mixer, ff = block.mixer, block.feed_forward
-    ways = {"qkv": ops.few_row_takes(rows, mixer.params["qkv_proj"], engine.dtype, ops.EPI_QKV, mixer.d),
-            "o": ops.few_row_takes(rows, mixer.params["o_proj"], engine.dtype),
-            "gate_up": ops.few_row_takes(rows, ff.params["gate_up_proj"], engine.dtype, ops.EPI_SWIGLU),
-            "down": ops.few_row_takes(rows, ff.params["down_proj"], engine.dtype),
-            "head": ops.few_row_takes(rows, engine.model.lm_head.params["weight"], engine.dtype, ops.EPI_PLAIN_F32)}
-    library = [name for name, kernel in ways.items() if not kernel]
-    return f"{ops.few_row_route} kernel" + (f", library for {'+'.join(library)}" if library else "")
+    products = {"qkv": (mixer.params["qkv_proj"], ops.EPI_QKV, mixer.d), "o": (mixer.params["o_proj"], ops.EPI_PLAIN_BF16, 0),
+                "gate_up": (ff.params["gate_up_proj"], ops.EPI_SWIGLU, 0), "down": (ff.params["down_proj"], ops.EPI_PLAIN_BF16, 0),
+                "head": (engine.model.lm_head.params["weight"], ops.EPI_PLAIN_F32, 0)}
+    library = [name for name, (w, mode, d) in products.items() if not ops.few_row_takes(rows, w, engine.dtype, mode, d)]
+    streamed = [name for name, (w, mode, d) in products.items()
+                if name not in library and mode != ops.EPI_QKV and ops.stream_takes(rows, w, engine.dtype, mode)]
+    return (f"{ops.few_row_route} kernel" + (f", streaming kernel for {'+'.join(streamed)}" if streamed else "")
+            + (f", library for {'+'.join(library)}" if library else ""))
 
 
 def build_engine(shape_name, layers, biggest, context):

@@ -630,13 +630,111 @@ def _few_row_out(m: int, n: int, mode: int, device) -> torch.Tensor:
     return torch.empty((m, n), dtype=torch.float32 if mode == EPI_PLAIN_F32 else torch.bfloat16, device=device)
 
 
+class _StreamParams(ctypes.Structure):
+    """Mirror of ``StreamParams`` in csrc/stream_linear.cu (same order, native alignment)."""
+    _fields_ = [("x", ctypes.c_void_p), ("x_rows", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+                ("residual_out", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("norm_w_f32", ctypes.c_int),
+                ("eps", ctypes.c_float), ("w", ctypes.c_void_p), ("M", ctypes.c_int), ("N", ctypes.c_int),
+                ("K", ctypes.c_int), ("mode", ctypes.c_int), ("out", ctypes.c_void_p),
+                ("post_residual", ctypes.c_void_p), ("post_sum_out", ctypes.c_void_p), ("post_stats", ctypes.c_void_p),
+                ("rw", ctypes.c_int), ("ks", ctypes.c_int), ("groups", ctypes.c_int), ("tiles", ctypes.c_int)]
+
+
+def _stream_lib():
+    lib = load_cuda_library("stream_linear.cu")
+    if not getattr(lib, "_checked", False):
+        if lib.b200_stream_params_size() != ctypes.sizeof(_StreamParams):
+            raise KernelError("the parameter block of stream_linear.cu and its Python mirror differ")
+        lib._checked = True
+    return lib
+
+
+# Few-row products on weights of at least this many bytes take the streaming kernel (every thread copies its own share
+# of the weights, one CTA an SM walks over many tiles: csrc/stream_linear.cu) instead of the ring kernel
+# (csrc/skinny_linear.cu), where the rows of x fit its shared memory: a rule of sizes, fixed by the environment or by
+# assignment, never by a measurement.  Measured in a decode step at batch 8: 4.28 -> 3.91 ms at the Qwen3-8B sizes
+# (gate/up and the head), 1.320 -> 1.308 ms at the Qwen3-0.6B sizes (the head); smaller matrices are faster on the
+# ring kernel (1.41 ms with the 0.6B gate/up here).
+stream_min_bytes = int(os.environ.get("LLM_INFER_B200_STREAM_MIN_BYTES", 64 << 20))
+
+
+def stream_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16) -> bool:
+    """Whether the streaming kernel can run this product: bfloat16 activations and weight, at most 16
+    rows that fit shared memory beside the weights on their way (8 rows of about 6,000 columns, 16 of about 3,000),
+    K a multiple of 32; plain or SwiGLU."""
+    if act_dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.dim() != 2:
+        return False
+    if not 0 < rows <= SKINNY_MAX_ROWS or weight.shape[1] % 32 or not weight.is_contiguous() or weight.data_ptr() % 16:
+        return False
+    if mode not in (EPI_PLAIN_BF16, EPI_PLAIN_F32, EPI_SWIGLU) or (mode == EPI_SWIGLU and weight.shape[0] % 2):
+        return False
+    return bool(_stream_lib().b200_stream_fits(mode, rows, weight.shape[0], weight.shape[1]))
+
+
+def stream_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16) -> bool:
+    """Whether a few-row product is routed to the streaming kernel."""
+    return (few_row_route == "single" and 2 * weight.shape[0] * weight.shape[1] >= stream_min_bytes
+            and stream_ok(rows, weight, act_dtype, mode))
+
+
+def stream_tile_cols(mode: int, m: int, n: int, k: int) -> int:
+    """Columns of the output that one tile of the streaming kernel covers for a product of ``m`` rows with
+    a weight [n, k] (its tiles of statistics)."""
+    return _stream_lib().b200_stream_tile_cols(mode, m, n, k)
+
+
+def stream_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None, norm_after=None, rw: int = 0, ks: int = 0) -> torch.Tensor:
+    """epilogue(prologue(x) . weight^T) for at most 16 rows and a large weight (csrc/stream_linear.cu).
+
+    ``x``: a bfloat16 tensor [rows, K] or a ``PendingNorm`` (with or without a residual); ``mode``: EPI_PLAIN_BF16,
+    EPI_PLAIN_F32 or EPI_SWIGLU; ``norm_after`` = (residual, sum_out, stats [tiles, 16]) as for ``skinny_linear``,
+    with tiles = ceil(N / ``stream_tile_cols(...)``); ``rw``, ``ks``: the launch's shape (groups of 16 weight rows a
+    tile: 1 or 2; warps that split K: up to 24), 0 for the launcher's choice.
+    """
+    _flush_held()
+    pending = x if isinstance(x, PendingNorm) else None
+    src = pending.x if pending is not None else x
+    rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
+    _cuda(src, weight, rows_t)
+    _contig(src, weight, rows_t)
+    m = src.shape[0] if rows_t is None else rows_t.numel()
+    n, k = weight.shape
+    if src.shape[-1] != k:
+        raise KernelError(f"the rows have {src.shape[-1]} columns, the weight has {k}")
+    if not stream_ok(m, weight, src.dtype, mode):
+        raise KernelError("the streaming product refuses this size or dtype")
+    P = _StreamParams()
+    P.x, P.x_rows = src.data_ptr(), (0 if rows_t is None else rows_t.data_ptr())
+    if pending is not None:
+        w = pending.weight
+        if w.numel() != k or w.dtype not in (torch.float32, torch.bfloat16) or not w.is_cuda:
+            raise KernelError("the norm weight must have K elements, bfloat16 or float32, on the device")
+        P.norm_w, P.norm_w_f32, P.eps = w.data_ptr(), int(w.dtype == torch.float32), pending.eps
+        if pending.residual is not None:
+            res = pending.residual
+            if res.dtype != torch.bfloat16 or res.shape != src.shape or not res.is_contiguous():
+                raise KernelError("the residual must be bfloat16, contiguous and have the shape of x")
+            P.residual = res.data_ptr()
+            P.residual_out = 0 if pending.residual_out is None else pending.residual_out.data_ptr()
+    P.w, P.M, P.N, P.K, P.mode = weight.data_ptr(), m, n, k, mode
+    if out is None:
+        out = _few_row_out(m, n, mode, src.device)
+    if norm_after is not None:
+        P.post_residual, P.post_sum_out, P.post_stats = (t.data_ptr() for t in norm_after)
+    P.out, P.rw, P.ks = out.data_ptr(), rw, ks
+    rc = _stream_lib().b200_stream_linear(ctypes.byref(P), _sm_count(src.device), _stream())
+    _ok(rc, "stream_linear")
+    return out
+
+
 # A lazy PLAIN bfloat16 product of the "single" route is held back until the next launch is known: if that is a
 # product behind an add + RMSNorm of this product's result, the held product's epilogue begins the norm (the rounded
 # sum and the rows' sums of squares), and the next product reads only its own columns instead of whole rows, which
 # every one of its CTAs would otherwise fetch (at 4,096 columns that read took 5 of a product's 20 us).
 class _Held:
-    def __init__(self, x, weight, x_rows, out):
-        self.x, self.weight, self.x_rows, self.out = x, weight, x_rows, out
+    def __init__(self, x, weight, x_rows, out, stream=False):
+        self.x, self.weight, self.x_rows, self.out, self.stream = x, weight, x_rows, out, stream
 
 
 _held: Optional[_Held] = None
@@ -649,36 +747,44 @@ def _flush_held(norm_after=None) -> None:
     if h is None:
         return
     _held = None
-    skinny_linear(h.x, h.weight, EPI_PLAIN_BF16, x_rows=h.x_rows, out=h.out, norm_after=norm_after)
+    if h.stream:
+        stream_linear(h.x, h.weight, EPI_PLAIN_BF16, x_rows=h.x_rows, out=h.out, norm_after=norm_after)
+    else:
+        skinny_linear(h.x, h.weight, EPI_PLAIN_BF16, x_rows=h.x_rows, out=h.out, norm_after=norm_after)
 
 
 def _single_lazy(x, weight, mode, x_rows, qkv, lazy) -> torch.Tensor:
     """The "single" route of ``few_row_linear``."""
     global _held
     pending = x if isinstance(x, PendingNorm) else None
+    src = pending.x if pending is not None else x
+    rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
+    m = src.shape[0] if rows_t is None else rows_t.numel()
+    to_stream = mode != EPI_QKV and src.is_cuda and stream_takes(m, weight, src.dtype, mode)
     h = _held
     stats = None
-    if (h is not None and pending is not None and pending.x is h.out and pending.residual is not None
+    # (the streaming kernel gets the rows' statistics from its own loop: nothing is handed to it)
+    if (h is not None and not to_stream and pending is not None and pending.x is h.out and pending.residual is not None
             and x_rows is None and pending.residual.dtype == torch.bfloat16
             and pending.residual.shape == h.out.shape and pending.residual.is_contiguous()):
-        lib = _skinny()
-        sms = _sm_count(h.out.device)
         n = h.weight.shape[0]
-        bn = lib.b200_skinny_tile_rows(EPI_PLAIN_BF16, 0, n, sms)
-        if bn <= 128:
-            tiles = -(-n // bn)
+        if h.stream:
+            cols = stream_tile_cols(EPI_PLAIN_BF16, h.out.shape[0], n, h.weight.shape[1])
+        else:
+            cols = _skinny().b200_skinny_tile_rows(EPI_PLAIN_BF16, 0, n, _sm_count(h.out.device))
+        if 0 < cols <= 128:
+            tiles = -(-n // cols)
             stat_t = torch.empty((tiles, SKINNY_MAX_ROWS), dtype=torch.float32, device=h.out.device)
             sum_out = pending.residual_out if pending.residual_out is not None else torch.empty_like(pending.residual)
             _flush_held((pending.residual, sum_out, stat_t))
             stats = (stat_t, tiles)
     _flush_held()
-    src = pending.x if pending is not None else x
-    rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
-    m = src.shape[0] if rows_t is None else rows_t.numel()
     if (lazy and mode == EPI_PLAIN_BF16 and stats is None and (pending is None or pending.residual is not None)
-            and src.is_cuda and skinny_ok(m, weight, src.dtype, mode)):
-        _held = _Held(x, weight, x_rows, _few_row_out(m, weight.shape[0], mode, src.device))
+            and src.is_cuda and (to_stream or skinny_ok(m, weight, src.dtype, mode))):
+        _held = _Held(x, weight, x_rows, _few_row_out(m, weight.shape[0], mode, src.device), stream=to_stream)
         return _held.out
+    if to_stream:
+        return stream_linear(x, weight, mode, x_rows=x_rows)
     return skinny_linear(x, weight, mode, x_rows=x_rows, qkv=qkv, stats=stats)
 
 
@@ -789,7 +895,11 @@ def few_row_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode:
     epilogue after it fused in) rather than as a library product with those as kernels of their own."""
     if few_row_route == "chain" and chain_takes(rows, weight, act_dtype, mode, head_dim):
         return True
-    if few_row_route == "library" or not skinny_ok(rows, weight, act_dtype, mode, head_dim):
+    if few_row_route == "library":
+        return False
+    if mode != EPI_QKV and stream_takes(rows, weight, act_dtype, mode):
+        return True
+    if not skinny_ok(rows, weight, act_dtype, mode, head_dim):
         return False
     # The single-product kernel gives every CTA the rows of x to normalise and one tile of 128 weight rows; on the
     # largest layer matrices (gate/up and down at the Qwen3-32B sizes, 262 and 524 MB) the library product with the norm
