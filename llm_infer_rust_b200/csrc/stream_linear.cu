@@ -72,6 +72,7 @@ struct StreamParams {
   // shape of the launch, 0: chosen by the launcher: groups of 16 weight rows a tile, warps that split K
   int rw, ks;
   int groups, tiles;        // (filled by the launcher: groups of KS warps a CTA, tiles of the product)
+  int xd;                   // the rows of x come with the weights' copies instead of waiting in shared memory: 1 yes, 0 no, -1 where they do not fit
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -113,10 +114,14 @@ constexpr int MAX_THREADS = 768;
 constexpr int TURN_BYTES = 64;         // weights that a thread fetches a turn: four asynchronous copies of 16 bytes
 constexpr int TURNS = 2;               // turns on their way (beside the one in registers): 128 bytes a thread, 96 KB an SM
 
-template <int RW, int NB, bool NORM>
+// XD: the rows of x are too long for shared memory (and have no norm before them): every thread fetches its own
+// 16 bytes of them a chunk with the weights' copies, from the second-level cache, where the few rows of x stay.
+template <int RW, int NB, bool NORM, bool XD>
 __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const StreamParams p) {
+  static_assert(!(NORM && XD), "the norm needs whole rows of x in shared memory");
   constexpr int U = TURN_BYTES / 32 / RW;      // chunks a turn
   constexpr int SLOTS = TURN_BYTES / 16;       // 16-byte pieces of weights that a thread fetches a turn
+  constexpr int TSLOTS = SLOTS + (XD ? U * NB : 0);   // ... and of the rows of x
   constexpr int LDR = Layout<NB>::LDR;
   constexpr int MP = NB * 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -126,8 +131,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
   const int K = p.K, M = p.M;
   const int row_bytes = xs_row_bytes(K);
   unsigned char* xs = smem_raw;
-  float* red = reinterpret_cast<float*>(xs + MP * row_bytes) + grp * KS * RW * 16 * LDR;
-  float* part = reinterpret_cast<float*>(xs + MP * row_bytes) + G * KS * RW * 16 * LDR;
+  const int xs_bytes = XD ? 0 : MP * row_bytes;
+  float* red = reinterpret_cast<float*>(xs + xs_bytes) + grp * KS * RW * 16 * LDR;
+  float* part = reinterpret_cast<float*>(xs + xs_bytes) + G * KS * RW * 16 * LDR;
   float* scale = part + G * KS * MMAX;
   // this thread's pieces: piece s of turn r at ((r * SLOTS + s) * threads + thread) * 16 (a warp's 32 pieces side by side)
   unsigned char* ring = reinterpret_cast<unsigned char*>(scale + MMAX) + threadIdx.x * 16;
@@ -165,7 +171,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
   // landed" always means "the turn to be multiplied now has landed".
   int itile = tile, ic = c_lo;
   if (itile < p.tiles) rows_of(itile);
-  auto issue = [&](int r) {
+  auto issue_w = [&](int r) {
     if (itile < p.tiles) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -174,7 +180,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
         for (int j = 0; j < RW; ++j)
 #pragma unroll
           for (int h = 0; h < 2; ++h)
-            cp_async16(ring + (r * SLOTS + (u * RW + j) * 2 + h) * piece_stride,
+            cp_async16(ring + (r * TSLOTS + (u * RW + j) * 2 + h) * piece_stride,
                        in ? p.w + (wrow[j][h] + static_cast<unsigned>(ic + u) * CHUNK) : p.w, in);
       }
       ic += U;
@@ -184,15 +190,53 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
         if (itile < p.tiles) rows_of(itile);
       }
     }
-    cp_async_commit();
+  };
+  // (XD) the same turn's pieces of the rows of x: row n = nb * 8 + g, the chunk's 16 bytes of thread t
+  int xtile = tile, xc = c_lo;
+  unsigned xoff[NB];
+  bool has[NB];
+  auto issue_x = [&](int r) {
+    if (XD && xtile < p.tiles) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const bool in = xc + u < c_hi && has[nb];
+          cp_async16(ring + (r * TSLOTS + SLOTS + u * NB + nb) * piece_stride,
+                     in ? p.x + (xoff[nb] + static_cast<unsigned>(xc + u) * CHUNK) : p.x, in);
+        }
+      xc += U;
+      if (xc >= c_hi) {
+        xc = c_lo;
+        xtile += stride;
+      }
+    }
   };
 #pragma unroll
-  for (int r = 0; r < TURNS; ++r) issue(r);
+  for (int r = 0; r < TURNS; ++r) {
+    issue_w(r);
+    if (!XD) cp_async_commit();
+  }
   pdl_wait();                       // x and the residual belong to the kernels before this one
+  if (XD) {
+    // (the first group then holds the weights of all first turns and the first turn's x: whoever waits for a turn's
+    // group has that turn's weights too)
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int n = nb * 8 + g;
+      has[nb] = n < M;
+      xoff[nb] = (has[nb] ? static_cast<unsigned>(p.x_rows ? p.x_rows[n] : n) * static_cast<unsigned>(K) : 0u) + 8u * t;
+    }
+#pragma unroll
+    for (int r = 0; r < TURNS; ++r) {
+      issue_x(r);
+      cp_async_commit();
+    }
+  }
 
   // ---- the rows of x' into shared memory, four rows at a time: a thread takes 16 bytes of each of them (their loads
   // are on their way together), so a row's sum of squares is spread over the threads and meets in `part`
-  {
+  if (!XD) {
     const bool writer = NORM && blockIdx.x == 0 && p.residual_out != nullptr;
 #pragma unroll 1
     for (int m0 = 0; m0 < MP; m0 += 4) {
@@ -285,13 +329,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
         for (int j = 0; j < RW; ++j)
 #pragma unroll
           for (int h = 0; h < 2; ++h)
-            wv[u][j][h] = *reinterpret_cast<const uint4*>(ring + (turn * SLOTS + (u * RW + j) * 2 + h) * piece_stride);
+            wv[u][j][h] = *reinterpret_cast<const uint4*>(ring + (turn * TSLOTS + (u * RW + j) * 2 + h) * piece_stride);
       uint4 xb[U][NB];
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb)
-          xb[u][nb] = c + u < c_hi ? *reinterpret_cast<const uint4*>(xme[nb] + (c + u) * (CHUNK * 2)) : make_uint4(0u, 0u, 0u, 0u);
+          xb[u][nb] = XD ? *reinterpret_cast<const uint4*>(ring + (turn * TSLOTS + SLOTS + u * NB + nb) * piece_stride)
+                         : c + u < c_hi ? *reinterpret_cast<const uint4*>(xme[nb] + (c + u) * (CHUNK * 2)) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
       for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -301,7 +346,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
             mma_16816(acc[j][nb], wv[u][j][0].x, wv[u][j][1].x, wv[u][j][0].y, wv[u][j][1].y, xb[u][nb].x, xb[u][nb].y);
             mma_16816(acc[j][nb], wv[u][j][0].z, wv[u][j][1].z, wv[u][j][0].w, wv[u][j][1].w, xb[u][nb].z, xb[u][nb].w);
           }
-      issue(turn);                             // (behind the multiplies: the pieces are in registers before they are overwritten)
+      issue_w(turn);                           // (behind the multiplies: the pieces are in registers before they are overwritten)
+      issue_x(turn);
+      cp_async_commit();
       turn = turn + 1 == TURNS ? 0 : turn + 1;
     }
     // ---- the warps' sums meet in shared memory
@@ -369,18 +416,24 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
 
 // ------------------------------------------------------------------ host side
 typedef void (*StreamKernel)(const StreamParams);
-static StreamKernel kernel_of(int rw, int nb, bool norm) {
-  if (rw == 1 && nb == 1) return norm ? stream_linear_kernel<1, 1, true> : stream_linear_kernel<1, 1, false>;
-  if (rw == 1 && nb == 2) return norm ? stream_linear_kernel<1, 2, true> : stream_linear_kernel<1, 2, false>;
-  if (rw == 2 && nb == 1) return norm ? stream_linear_kernel<2, 1, true> : stream_linear_kernel<2, 1, false>;
-  if (rw == 2 && nb == 2) return norm ? stream_linear_kernel<2, 2, true> : stream_linear_kernel<2, 2, false>;
+template <int RW, int NB>
+static StreamKernel kernel_of(bool norm, bool xd) {
+  if (norm) return stream_linear_kernel<RW, NB, true, false>;
+  return xd ? stream_linear_kernel<RW, NB, false, true> : stream_linear_kernel<RW, NB, false, false>;
+}
+static StreamKernel kernel_of(int rw, int nb, bool norm, bool xd) {
+  if (rw == 1 && nb == 1) return kernel_of<1, 1>(norm, xd);
+  if (rw == 1 && nb == 2) return kernel_of<1, 2>(norm, xd);
+  if (rw == 2 && nb == 1) return kernel_of<2, 1>(norm, xd);
+  if (rw == 2 && nb == 2) return kernel_of<2, 2>(norm, xd);
   return nullptr;
 }
-// Shared memory of a CTA of `warps` warps.
-static size_t smem_of(int rw, int nb, int k, int warps) {
-  return static_cast<size_t>(nb) * 8 * xs_row_bytes(k) +
+// Shared memory of a CTA of `warps` warps: the rows of x' (not with xd), the warps' sums, the statistics, the pieces.
+static size_t smem_of(int rw, int nb, int k, int warps, bool xd) {
+  const int u = TURN_BYTES / 32 / rw;
+  return (xd ? 0 : static_cast<size_t>(nb) * 8 * xs_row_bytes(k)) +
          (static_cast<size_t>(warps) * rw * 16 * (nb * 8 + 2) + warps * MMAX + MMAX) * sizeof(float) +
-         static_cast<size_t>(warps) * 32 * TURNS * TURN_BYTES;
+         static_cast<size_t>(warps) * 32 * TURNS * (TURN_BYTES + (xd ? u * nb * 16 : 0));
 }
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
@@ -394,36 +447,41 @@ static int choose_ks(int k) {
   return 2;
 }
 
-// Groups of 16 weight rows a tile for a plain product: 0 if the product is refused (the rows of x do not fit).
-static int shape_of(const StreamParams& p, int nb, int* ks_out, int* groups_out) {
+// The shape of the launch: groups of 16 weight rows a tile (0: the product is refused), warps that split K, groups of
+// them a CTA, and whether the rows of x come with the weights' copies (they do not fit shared memory; p.xd forces it).
+static int shape_of(const StreamParams& p, int nb, bool norm, int* ks_out, int* groups_out, bool* xd_out) {
   const int rw = p.rw > 0 ? p.rw : (p.mode == EPI_SWIGLU ? 2 : 1);
-  int ks = p.ks > 0 ? p.ks : choose_ks(p.K);
-  if (ks > MAX_THREADS / 32) return 0;
+  const int ks = p.ks > 0 ? p.ks : choose_ks(p.K);
+  if (ks > MAX_THREADS / 32 || rw > 2) return 0;
   int groups = MAX_THREADS / 32 / ks;
   if (groups > 12) groups = 12;
   *ks_out = ks;
   *groups_out = groups;
-  return smem_of(rw, nb, p.K, ks * groups) <= SMEM_LIMIT ? rw : 0;
+  const bool staged_fits = smem_of(rw, nb, p.K, ks * groups, false) <= SMEM_LIMIT;
+  *xd_out = !norm && (p.xd > 0 || (p.xd < 0 && !staged_fits));
+  if (!*xd_out) return staged_fits ? rw : 0;
+  return smem_of(rw, nb, p.K, ks * groups, true) <= SMEM_LIMIT ? rw : 0;
 }
 
 // Whether the kernel takes a product of m rows with a weight [n, k] (the rows of x must fit shared memory).
-B200_EXPORT int b200_stream_fits(int mode, int m, int n, int k) {
+B200_EXPORT int b200_stream_fits(int mode, int m, int n, int k, int norm) {
   if (k <= 0 || k % CHUNK != 0 || n <= 0 || m <= 0 || m > MMAX || mode < EPI_PLAIN_BF16 || mode > EPI_SWIGLU) return 0;
   if (static_cast<long long>(n) * k >= (1ll << 32)) return 0;
   StreamParams p = {};
-  p.M = m; p.N = n; p.K = k; p.mode = mode;
+  p.M = m; p.N = n; p.K = k; p.mode = mode; p.xd = -1;
   int ks, groups;
-  return shape_of(p, m <= 8 ? 1 : 2, &ks, &groups) > 0 ? 1 : 0;
+  bool xd;
+  return shape_of(p, m <= 8 ? 1 : 2, norm != 0, &ks, &groups, &xd) > 0 ? 1 : 0;
 }
 
 // Columns of the output that one tile covers for a product [m, n] x [n, k] (the tiles of post_stats): 0 if refused.
-B200_EXPORT int b200_stream_tile_cols(int mode, int m, int n, int k) {
-  if (!b200_stream_fits(mode, m, n, k)) return 0;
+B200_EXPORT int b200_stream_tile_cols(int mode, int m, int n, int k, int norm) {
+  if (!b200_stream_fits(mode, m, n, k, norm)) return 0;
   return 16;
 }
 
 // `params`: a StreamParams filled by the caller.  Refuses (B200_BAD_SIZE) more than 16 rows, a K that is no multiple
-// of 32, rows of x that do not fit shared memory, a matrix of 2^32 elements or more, an odd N with SwiGLU, a residual
+// of 32, rows of x behind a norm that do not fit shared memory, a matrix of 2^32 elements or more, an odd N with SwiGLU, a residual
 // without a norm, and shapes of the launch that the kernel does not have (rw 1 or 2, SwiGLU 2; ks up to 24).
 B200_EXPORT int b200_stream_linear(const void* params, int sm_count, cudaStream_t stream) {
   StreamParams p;
@@ -444,14 +502,15 @@ B200_EXPORT int b200_stream_linear(const void* params, int sm_count, cudaStream_
   const int nb = p.M <= 8 ? 1 : 2;
   const bool norm = p.norm_w != nullptr;
   int ks = 0, groups = 0;
-  const int rw = shape_of(p, nb, &ks, &groups);
-  StreamKernel kernel = kernel_of(rw, nb, norm);
+  bool xd = false;
+  const int rw = shape_of(p, nb, norm, &ks, &groups, &xd);
+  StreamKernel kernel = kernel_of(rw, nb, norm, xd);
   if (rw == 0 || kernel == nullptr || ks < 1 || (swiglu && rw != 2) || (post && rw != 1)) return B200_BAD_SIZE;
   const int cols = swiglu ? p.N / 2 : p.N;
   const int tile_cols = swiglu ? 16 : rw * 16;
   p.rw = rw; p.ks = ks; p.groups = groups;
   p.tiles = (cols + tile_cols - 1) / tile_cols;
-  const size_t smem = smem_of(rw, nb, p.K, ks * groups);
+  const size_t smem = smem_of(rw, nb, p.K, ks * groups, xd);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_LIMIT));
   if (e != cudaSuccess) return static_cast<int>(e);
   const int sms = sm_count > 0 ? sm_count : 148;

@@ -637,7 +637,8 @@ class _StreamParams(ctypes.Structure):
                 ("eps", ctypes.c_float), ("w", ctypes.c_void_p), ("M", ctypes.c_int), ("N", ctypes.c_int),
                 ("K", ctypes.c_int), ("mode", ctypes.c_int), ("out", ctypes.c_void_p),
                 ("post_residual", ctypes.c_void_p), ("post_sum_out", ctypes.c_void_p), ("post_stats", ctypes.c_void_p),
-                ("rw", ctypes.c_int), ("ks", ctypes.c_int), ("groups", ctypes.c_int), ("tiles", ctypes.c_int)]
+                ("rw", ctypes.c_int), ("ks", ctypes.c_int), ("groups", ctypes.c_int), ("tiles", ctypes.c_int),
+                ("xd", ctypes.c_int)]
 
 
 def _stream_lib():
@@ -658,39 +659,53 @@ def _stream_lib():
 stream_min_bytes = int(os.environ.get("LLM_INFER_B200_STREAM_MIN_BYTES", 64 << 20))
 
 
-def stream_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16) -> bool:
-    """Whether the streaming kernel can run this product: bfloat16 activations and weight, at most 16
-    rows that fit shared memory beside the weights on their way (8 rows of about 6,000 columns, 16 of about 3,000),
-    K a multiple of 32; plain or SwiGLU."""
+def stream_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
+              norm: bool = True) -> bool:
+    """Whether the streaming kernel can run this product: bfloat16 activations and weight, at most 16 rows, K a
+    multiple of 32; plain or SwiGLU.  Behind a norm (``norm``) the rows must fit its shared memory beside the weights
+    on their way (8 rows of about 6,000 columns, 16 of about 3,000); without one, longer rows come with the weights'
+    copies."""
     if act_dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.dim() != 2:
         return False
     if not 0 < rows <= SKINNY_MAX_ROWS or weight.shape[1] % 32 or not weight.is_contiguous() or weight.data_ptr() % 16:
         return False
     if mode not in (EPI_PLAIN_BF16, EPI_PLAIN_F32, EPI_SWIGLU) or (mode == EPI_SWIGLU and weight.shape[0] % 2):
         return False
-    return bool(_stream_lib().b200_stream_fits(mode, rows, weight.shape[0], weight.shape[1]))
+    return bool(_stream_lib().b200_stream_fits(mode, rows, weight.shape[0], weight.shape[1], int(norm)))
 
 
-def stream_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16) -> bool:
-    """Whether a few-row product is routed to the streaming kernel."""
-    return (few_row_route == "single" and 2 * weight.shape[0] * weight.shape[1] >= stream_min_bytes
-            and stream_ok(rows, weight, act_dtype, mode))
+def stream_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
+                 norm: bool = True) -> bool:
+    """Whether a few-row product (behind a norm or not) is routed to the streaming kernel: a weight of
+    ``stream_min_bytes`` or more, and rows of x that fit the kernel's shared memory; rows that do not fit (and have no
+    norm before them) only for more than 8 rows of a weight that the ring kernel would else take, since it falls off
+    there (Qwen3-8B down projection, 16 rows: 22.8 against 37.4 us, a decode step at batch 16 6.36 -> 5.96 ms; with 8
+    rows 20.2 against 21.3 us alone and a decode step no faster for it; the Qwen3-32B down projection is faster on
+    the library: 49 against 64 us)."""
+    nbytes = 2 * weight.shape[0] * weight.shape[1]
+    if few_row_route != "single" or nbytes < stream_min_bytes:
+        return False
+    if stream_ok(rows, weight, act_dtype, mode, True):
+        return True
+    return not norm and rows > 8 and nbytes < single_max_bytes and stream_ok(rows, weight, act_dtype, mode, False)
 
 
-def stream_tile_cols(mode: int, m: int, n: int, k: int) -> int:
-    """Columns of the output that one tile of the streaming kernel covers for a product of ``m`` rows with
-    a weight [n, k] (its tiles of statistics)."""
-    return _stream_lib().b200_stream_tile_cols(mode, m, n, k)
+def stream_tile_cols(mode: int, m: int, n: int, k: int, norm: bool) -> int:
+    """Columns of the output that one tile of the streaming kernel covers for a product of ``m`` rows with a weight
+    [n, k] (its tiles of statistics)."""
+    return _stream_lib().b200_stream_tile_cols(mode, m, n, k, int(norm))
 
 
 def stream_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
-                  out: Optional[torch.Tensor] = None, norm_after=None, rw: int = 0, ks: int = 0) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, norm_after=None, rw: int = 0, ks: int = 0,
+                  xd: int = -1) -> torch.Tensor:
     """epilogue(prologue(x) . weight^T) for at most 16 rows and a large weight (csrc/stream_linear.cu).
 
     ``x``: a bfloat16 tensor [rows, K] or a ``PendingNorm`` (with or without a residual); ``mode``: EPI_PLAIN_BF16,
     EPI_PLAIN_F32 or EPI_SWIGLU; ``norm_after`` = (residual, sum_out, stats [tiles, 16]) as for ``skinny_linear``,
     with tiles = ceil(N / ``stream_tile_cols(...)``); ``rw``, ``ks``: the launch's shape (groups of 16 weight rows a
-    tile: 1 or 2; warps that split K: up to 24), 0 for the launcher's choice.
+    tile: 1 or 2; warps that split K: up to 24), 0 for the launcher's choice; ``xd``: whether the rows of x come with
+    the weights' copies instead of waiting in shared memory (1, 0, or -1: where they do not fit; never behind a norm).
     """
     _flush_held()
     pending = x if isinstance(x, PendingNorm) else None
@@ -702,7 +717,7 @@ def stream_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     n, k = weight.shape
     if src.shape[-1] != k:
         raise KernelError(f"the rows have {src.shape[-1]} columns, the weight has {k}")
-    if not stream_ok(m, weight, src.dtype, mode):
+    if not stream_ok(m, weight, src.dtype, mode, pending is not None):
         raise KernelError("the streaming product refuses this size or dtype")
     P = _StreamParams()
     P.x, P.x_rows = src.data_ptr(), (0 if rows_t is None else rows_t.data_ptr())
@@ -722,7 +737,7 @@ def stream_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
         out = _few_row_out(m, n, mode, src.device)
     if norm_after is not None:
         P.post_residual, P.post_sum_out, P.post_stats = (t.data_ptr() for t in norm_after)
-    P.out, P.rw, P.ks = out.data_ptr(), rw, ks
+    P.out, P.rw, P.ks, P.xd = out.data_ptr(), rw, ks, xd
     rc = _stream_lib().b200_stream_linear(ctypes.byref(P), _sm_count(src.device), _stream())
     _ok(rc, "stream_linear")
     return out
@@ -760,7 +775,7 @@ def _single_lazy(x, weight, mode, x_rows, qkv, lazy) -> torch.Tensor:
     src = pending.x if pending is not None else x
     rows_t = pending.rows if pending is not None and pending.rows is not None else x_rows
     m = src.shape[0] if rows_t is None else rows_t.numel()
-    to_stream = mode != EPI_QKV and src.is_cuda and stream_takes(m, weight, src.dtype, mode)
+    to_stream = mode != EPI_QKV and src.is_cuda and stream_takes(m, weight, src.dtype, mode, pending is not None)
     h = _held
     stats = None
     # (the streaming kernel gets the rows' statistics from its own loop: nothing is handed to it)
@@ -769,7 +784,7 @@ def _single_lazy(x, weight, mode, x_rows, qkv, lazy) -> torch.Tensor:
             and pending.residual.shape == h.out.shape and pending.residual.is_contiguous()):
         n = h.weight.shape[0]
         if h.stream:
-            cols = stream_tile_cols(EPI_PLAIN_BF16, h.out.shape[0], n, h.weight.shape[1])
+            cols = stream_tile_cols(EPI_PLAIN_BF16, h.out.shape[0], n, h.weight.shape[1], isinstance(h.x, PendingNorm))
         else:
             cols = _skinny().b200_skinny_tile_rows(EPI_PLAIN_BF16, 0, n, _sm_count(h.out.device))
         if 0 < cols <= 128:
@@ -890,14 +905,15 @@ def chain_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: i
 
 
 def few_row_takes(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
-                  head_dim: int = 0) -> bool:
+                  head_dim: int = 0, norm: bool = True) -> bool:
     """Whether a product of ``rows`` rows runs on this package's few-row kernels (with the norm before it and the
-    epilogue after it fused in) rather than as a library product with those as kernels of their own."""
+    epilogue after it fused in) rather than as a library product with those as kernels of their own.  ``norm``: the
+    product may come behind a norm (False: its input is a plain tensor)."""
     if few_row_route == "chain" and chain_takes(rows, weight, act_dtype, mode, head_dim):
         return True
     if few_row_route == "library":
         return False
-    if mode != EPI_QKV and stream_takes(rows, weight, act_dtype, mode):
+    if mode != EPI_QKV and stream_takes(rows, weight, act_dtype, mode, norm):
         return True
     if not skinny_ok(rows, weight, act_dtype, mode, head_dim):
         return False
@@ -1157,7 +1173,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         if out_dtype in (torch.bfloat16, torch.float32) and x.dim() == 2 and x.is_contiguous() and x.is_cuda:
             mode = EPI_PLAIN_F32 if out_dtype == torch.float32 else EPI_PLAIN_BF16
-            if few_row_takes(x.shape[0], weight, x.dtype, mode):
+            if few_row_takes(x.shape[0], weight, x.dtype, mode, norm=False):
                 return few_row_linear(x, weight, mode, lazy=lazy)
         _cuda(x, weight)
         if out_dtype == torch.bfloat16:

@@ -58,13 +58,41 @@ def test_stream_product_plain(m, n, k, norm):
                 else:
                     src = o.PendingNorm(xs, rs if norm == "add" else None, nw if rw != 2 else nw.float(), 1e-5,
                                         rows=rows if gather else None, write_residual=not gather)
-                got = o.stream_linear(src, w, mode, x_rows=rows if (gather and norm == "none") else None, rw=rw, ks=ks)
-                assert got.dtype == dtype and tuple(got.shape) == (m, n)
-                tol = 2e-3 * scale if dtype == torch.float32 else 2.0 ** -7 * scale
-                assert (got.float() - want).abs().max() <= tol, (mode, gather, rw, ks)
+                # without a norm also with the rows of x fetched beside the weights (as rows too long for shared memory are)
+                for xd in ((0, 1) if norm == "none" else (-1,)):
+                    got = o.stream_linear(src, w, mode, x_rows=rows if (gather and norm == "none") else None, rw=rw, ks=ks, xd=xd)
+                    assert got.dtype == dtype and tuple(got.shape) == (m, n)
+                    tol = 2e-3 * scale if dtype == torch.float32 else 2.0 ** -7 * scale
+                    assert (got.float() - want).abs().max() <= tol, (mode, gather, rw, ks, xd)
                 if norm == "add" and not gather:
                     assert torch.equal(src.residual_out, s_sum.to(torch.bfloat16))     # the rounded sum is the new residual
                     assert torch.equal(src.residual, res[:m])                          # the old one is left alone
+    o.check_errors(torch.device(DEV))
+
+
+@pytest.mark.parametrize("m,n,k", [(3, 96, 12288), (16, 4100, 12288), (8, 40, 25600)])
+def test_stream_product_with_rows_too_long_for_shared_memory(m, n, k):
+    """Rows of x that do not fit shared memory (and have no norm before them) come with the weights' copies; the
+    product that follows behind a norm gets its beginning all the same."""
+    o = ops()
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, seed=1, scale=0.05)
+    assert not o.stream_ok(m, w, torch.bfloat16, norm=True) and o.stream_ok(m, w, torch.bfloat16, norm=False)
+    want = x.float() @ w.float().t()
+    scale = max(1.0, float(want.abs().max()))
+    for rw, ks in [(0, 0), (1, 24), (1, 5), (2, 12)]:
+        got = o.stream_linear(x, w, o.EPI_PLAIN_F32, rw=rw, ks=ks)
+        assert (got - want).abs().max() <= 2e-3 * scale, (rw, ks)
+    res = rnd(m, n, dtype=torch.bfloat16, seed=2)
+    cols = o.stream_tile_cols(o.EPI_PLAIN_BF16, m, n, k, False)
+    tiles = -(-n // cols)
+    sum_out, stats = torch.empty_like(res), torch.zeros(tiles, 16, device=DEV)
+    got = o.stream_linear(x, w, o.EPI_PLAIN_BF16, norm_after=(res, sum_out, stats))
+    assert (got.float() - want).abs().max() <= 2.0 ** -7 * scale
+    s_sum = got.float() + res.float()
+    assert torch.equal(sum_out, s_sum.to(torch.bfloat16))
+    torch.testing.assert_close(stats[:, :m].sum(0), (s_sum * s_sum).sum(-1), rtol=1e-4, atol=1e-3)
+    with pytest.raises(o.KernelError):
+        o.stream_linear(o.PendingNorm(x, None, torch.ones(k, dtype=torch.bfloat16, device=DEV), 1e-6), w)
     o.check_errors(torch.device(DEV))
 
 
@@ -82,7 +110,7 @@ def test_stream_product_swiglu(m, inter, k, with_norm):
     want = R.ref_silu_mul(_bf(gu).to(torch.bfloat16))
     for rw, ks in [(0, 0), (2, 8), (2, 3), (2, 24), (2, 1)]:
         src = o.PendingNorm(x, res, nw, 1e-6) if with_norm else x
-        got = o.stream_linear(src, w, o.EPI_SWIGLU, rw=rw, ks=ks)
+        got = o.stream_linear(src, w, o.EPI_SWIGLU, rw=rw, ks=ks, xd=-1 if with_norm else ks % 2)
         assert tuple(got.shape) == (m, inter)
         assert (got.float() - want.float()).abs().max() <= 2.0 ** -6 * max(1.0, float(want.float().abs().max())), (rw, ks)
     o.check_errors(torch.device(DEV))
@@ -108,7 +136,8 @@ def test_routed_products_hand_the_norm_from_one_to_the_next(monkeypatch, m, k0, 
         pytest.skip("the streaming kernel takes K in multiples of 32")
     # a rule of sizes routes: make it say what this case wants
     big = {id(w): name == "stream" for w, name in ((w1, first), (w2, second))}
-    monkeypatch.setattr(o, "stream_takes", lambda rows, weight, dtype, mode=o.EPI_PLAIN_BF16: big.get(id(weight), False))
+    monkeypatch.setattr(o, "stream_takes",
+                        lambda rows, weight, dtype, mode=o.EPI_PLAIN_BF16, norm=True: big.get(id(weight), False))
 
     def second_product(src):
         if kind == "plain":
@@ -173,4 +202,5 @@ def test_stream_product_rule_and_refusals():
     assert o.stream_ok(8, rnd(16, 6016, dtype=torch.bfloat16), torch.bfloat16)
     assert not o.stream_ok(9, rnd(16, 6016, dtype=torch.bfloat16), torch.bfloat16)            # 16 rows of x do not fit
     assert not o.stream_ok(8, rnd(16, 12288, dtype=torch.bfloat16), torch.bfloat16)
+    assert o.stream_ok(16, rnd(16, 12288, dtype=torch.bfloat16), torch.bfloat16, norm=False)  # (they come with the weights)
     o.check_errors(torch.device(DEV))
