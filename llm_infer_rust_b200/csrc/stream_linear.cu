@@ -20,7 +20,7 @@
 //   x         the rows of x' (at most 16) wait in shared memory, as in skinny_linear.cu: ONE CTA an SM stages them
 //             once and then walks over many tiles of weight rows.
 //   split     the CTA's warps are G groups of KS warps.  A group owns a tile of RW x 16 weight rows at a time
-//             (SwiGLU: 16 gate rows and the same up rows); its KS warps split K (warp s takes the chunks
+//             (SwiGLU: 8 or 16 gate rows and the same up rows); its KS warps split K (warp s takes the chunks
 //             [s C / KS, (s+1) C / KS)), leave their sums in shared memory, and the group's epilogue adds them in
 //             warp order, so the result does not depend on timing.  Tiles are dealt out round-robin over all groups
 //             of all CTAs; the copies run two turns ahead across tiles, so a tile's epilogue has the next tile's
@@ -155,7 +155,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
 #pragma unroll
     for (int j = 0; j < RW; ++j) {
       int r0, limit;
-      if (swiglu) {                            // (RW = 2: gate rows, then up rows)
+      if (swiglu && RW == 1) {                 // 8 gate rows as the instruction's rows 0..7, the same up rows as its rows 8..15
+        wrow[j][0] = static_cast<unsigned>(min(tl * 8 + g, inter - 1)) * static_cast<unsigned>(K) + 8u * t;
+        wrow[j][1] = static_cast<unsigned>(min(inter + tl * 8 + g, p.N - 1)) * static_cast<unsigned>(K) + 8u * t;
+        continue;
+      }
+      if (swiglu) {                            // (RW = 2: 16 gate rows, then the same up rows)
         r0 = (j == 0 ? 0 : inter) + tl * 16;
         limit = j == 0 ? inter : p.N;
       } else {
@@ -400,7 +405,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
         }
       }
     } else {
-      constexpr int COLS = 16;
+      constexpr int COLS = RW == 1 ? 8 : 16;   // (the up rows' sums lie COLS rows behind the gate rows')
       for (int i = gt; i < M * COLS; i += gthreads) {
         const int m = i / COLS, rr = i - m * COLS, col = tile * COLS + rr;
         if (col >= inter) continue;
@@ -437,13 +442,14 @@ static size_t smem_of(int rw, int nb, int k, int warps, bool xd) {
 }
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
-// Warps of a group (they split K): every warp wants a handful of chunks a tile, and a group's epilogue costs the same
-// however few its warps; twelve groups at most (a barrier each).
+// Warps of a group (they split K): every warp wants at least six chunks a tile (Qwen3-32B gate/up, 160 chunks: 91 us
+// with 24 warps a group, 98 with 12; Qwen3-8B gate/up, 128 chunks: 40.4 with 24, 38.9 with 12); twelve groups at most
+// (a barrier each).
 static int choose_ks(int k) {
   const int chunks = k / CHUNK;
   const int choices[] = {24, 12, 8, 6, 4, 3, 2};
   for (int ks : choices)
-    if (chunks / ks >= 8) return ks;
+    if (chunks / ks >= 6) return ks;
   return 2;
 }
 
@@ -482,7 +488,7 @@ B200_EXPORT int b200_stream_tile_cols(int mode, int m, int n, int k, int norm) {
 
 // `params`: a StreamParams filled by the caller.  Refuses (B200_BAD_SIZE) more than 16 rows, a K that is no multiple
 // of 32, rows of x behind a norm that do not fit shared memory, a matrix of 2^32 elements or more, an odd N with SwiGLU, a residual
-// without a norm, and shapes of the launch that the kernel does not have (rw 1 or 2, SwiGLU 2; ks up to 24).
+// without a norm, and shapes of the launch that the kernel does not have (rw 1 or 2; ks up to 24).
 B200_EXPORT int b200_stream_linear(const void* params, int sm_count, cudaStream_t stream) {
   StreamParams p;
   memcpy(&p, params, sizeof(p));
@@ -505,14 +511,22 @@ B200_EXPORT int b200_stream_linear(const void* params, int sm_count, cudaStream_
   bool xd = false;
   const int rw = shape_of(p, nb, norm, &ks, &groups, &xd);
   StreamKernel kernel = kernel_of(rw, nb, norm, xd);
-  if (rw == 0 || kernel == nullptr || ks < 1 || (swiglu && rw != 2) || (post && rw != 1)) return B200_BAD_SIZE;
+  if (rw == 0 || kernel == nullptr || ks < 1 || (post && rw != 1)) return B200_BAD_SIZE;
   const int cols = swiglu ? p.N / 2 : p.N;
-  const int tile_cols = swiglu ? 16 : rw * 16;
+  const int tile_cols = swiglu ? rw * 8 : rw * 16;
   p.rw = rw; p.ks = ks; p.groups = groups;
   p.tiles = (cols + tile_cols - 1) / tile_cols;
   const size_t smem = smem_of(rw, nb, p.K, ks * groups, xd);
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_LIMIT));
-  if (e != cudaSuccess) return static_cast<int>(e);
+  // (once per kernel and device: the attribute belongs to the device's copy of the kernel)
+  static bool configured[8][2][2][3];                  // [device][rw][nb][norm / plain / plain with xd]
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 8) device = 0;
+  bool& done = configured[device][rw - 1][nb - 1][norm ? 0 : xd ? 2 : 1];
+  if (!done) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_LIMIT));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    done = true;
+  }
   const int sms = sm_count > 0 ? sm_count : 148;
   const int ctas = (p.tiles + groups - 1) / groups < sms ? (p.tiles + groups - 1) / groups : sms;
   return b200_launch(kernel, dim3(ctas), dim3(ks * groups * 32), smem, stream, 0, p);

@@ -108,7 +108,7 @@ def test_stream_product_swiglu(m, inter, k, with_norm):
     else:
         gu = x.float() @ w.float().t()
     want = R.ref_silu_mul(_bf(gu).to(torch.bfloat16))
-    for rw, ks in [(0, 0), (2, 8), (2, 3), (2, 24), (2, 1)]:
+    for rw, ks in [(0, 0), (2, 8), (2, 3), (2, 24), (2, 1), (1, 8), (1, 5), (1, 24)]:
         src = o.PendingNorm(x, res, nw, 1e-6) if with_norm else x
         got = o.stream_linear(src, w, o.EPI_SWIGLU, rw=rw, ks=ks, xd=-1 if with_norm else ks % 2)
         assert tuple(got.shape) == (m, inter)
@@ -193,8 +193,6 @@ def test_stream_product_rule_and_refusals():
     x = rnd(4, 64, dtype=torch.bfloat16)
     with pytest.raises(o.KernelError):
         o.stream_linear(rnd(17, 64, dtype=torch.bfloat16), w)
-    with pytest.raises(o.KernelError):
-        o.stream_linear(x, w, o.EPI_SWIGLU, rw=1, ks=4)                                        # SwiGLU needs gate and up rows
     with pytest.raises(o.KernelError):
         o.stream_linear(x, w, rw=3, ks=4)
     with pytest.raises(o.KernelError):
