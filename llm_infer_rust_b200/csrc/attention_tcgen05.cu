@@ -17,8 +17,8 @@
 //                  maximum has grown by more than 2^8 (then the row's thread rescales its O in tensor memory,
 //                  tcgen05.ld / st, once P V of the block before is finished); a stale reference is exact, since
 //                  the row sum uses the same one.
-// One warp fetches K blocks (ring of three) and V blocks (ring of two) by TMA; one warp owns tensor memory and
-// issues the MMAs.  Semantics as attention.cu (reference: src/models/attention/backend.rs:1455-1498): causal
+// Two warps (one in the two-tile kernel) fetch K blocks (ring of three) and V blocks (ring of two) by TMA, a page's
+// box each in turn; one warp owns tensor memory and issues the MMAs.  Semantics as attention.cu (reference: src/models/attention/backend.rs:1455-1498): causal
 // mask, optional window, scale as a parameter, softmax in float.  Value rows at or beyond what the tile may see are
 // zeroed in shared memory before they are used.  Every wait is bounded by the clock; on a time-out the error word
 // is flagged and every path still reaches the end, where tensor memory is given back.
@@ -40,8 +40,13 @@ constexpr int BKV = 128;                 // keys per block
 constexpr int HALF = BKV * 128;          // bytes of a [128 rows x 64 columns] half tile
 constexpr int TILE = 2 * HALF;           // bytes of a [128 x 128] bfloat16 tile
 constexpr int K_STAGES = 3, V_STAGES = 2;
-constexpr int THREADS = 192;             // one tile per CTA: warp 0 copies, warp 1 MMA, warps 2-5 softmax
-constexpr int PAIR_THREADS = 320;        // two tiles per CTA: four more softmax warps
+// Warps that issue the copies: warp 0 and the warps behind the softmax warps.  Measured (kernel alone, pages of 16 keys):
+// the one-tile kernel with 1 / 2 / 4 / 8 copy warps: 48.1 / 43.3 / 43.7 / 45.3 us at 2,048 tokens x 16 heads and 594 /
+// 740 / 709 / 673 TFLOP/s at 16,384 x 32; the two-tile kernel, which fetches half as much a query: 892 / 886 / 869 / 801.
+constexpr int COPY_WARPS = 2;
+constexpr int PAIR_COPY_WARPS = 1;
+constexpr int THREADS = 192 + 32 * (COPY_WARPS - 1);   // one tile per CTA: warp 0 copies, warp 1 MMA, warps 2-5 softmax, warps 6.. copy
+constexpr int PAIR_THREADS = 320 + 32 * (PAIR_COPY_WARPS - 1);   // two tiles per CTA: four more softmax warps (2-9), warps 10.. copy
 constexpr int TMEM_COLS = 512;           // S buffers (and P in their first 64 columns): columns 0..127 and 128..255; O: 256..383
 constexpr float RESCALE_STEP = 8.0f;     // the reference maximum follows only growth beyond 2^8
 
@@ -362,24 +367,29 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int nblk = active ? (kv_end - k_begin + BKV - 1) / BKV : 0;
   const int* table = block_table + static_cast<size_t>(row) * table_stride;
 
-  if (warp == 0) {
-    // ---- copies: lane j fetches the sub-blocks j, j + 32, ... (box_rows keys each) of a block of 128 keys.
+  if (warp == 0 || warp >= 6) {
+    // ---- copies: COPY_WARPS warps share a block's sub-blocks (box_rows keys each): warp c's lane l fetches the
+    // sub-blocks c + COPY_WARPS l, ...  (One SM takes in more through boxes that several warps issue than through
+    // as many from one warp: 34 to 37 against 23 GB/s in a probe that only copies pages of 16 keys; all copy warps
+    // walk the same stages and wait for the same barriers, the first announces a stage's bytes.  A box that lands
+    // before its stage's bytes are announced is no harm: the phase cannot end before the announcing arrival.)
     // Keys run one block further ahead than values (three stages against two): S of block i + 2 is wanted
     // while block i is still in the softmax.
     // The row's page numbers for this tile's keys come into shared memory first: a copy then does not begin with a
     // load from global memory whose answer it needs for its address.
+    const int cw = warp == 0 ? 0 : warp - 5;
     bool ok = true;
     int* tbl = reinterpret_cast<int*>(sm + TBL_OFF);
     const int first_page = k_begin / page_size;
     const int n_pages = min(TBL_ENTRIES, (kv_end + page_size - 1) / page_size - first_page);
-    for (int t = lane; t < n_pages; t += 32) tbl[t] = table[first_page + t];
-    __syncwarp();
+    for (int t = cw * 32 + lane; t < n_pages; t += 32 * COPY_WARPS) tbl[t] = table[first_page + t];
+    asm volatile("bar.sync 1, %0;\n" ::"n"(32 * COPY_WARPS) : "memory");      // (the copy warps only)
     auto fetch = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int first_key) {
       const int n_sub = (min(BKV, kv_end - first_key) + box_rows - 1) / box_rows;
       proxy_fence();
-      if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * box_rows * 128u);
+      if (cw == 0 && lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * box_rows * 128u);
       __syncwarp();
-      for (int j = lane; j < n_sub; j += 32) {
+      for (int j = cw + COPY_WARPS * lane; j < n_sub; j += 32 * COPY_WARPS) {
         const int key0 = first_key + j * box_rows;
         const int pi = key0 / page_size - first_page;
         const int page = pi < TBL_ENTRIES ? tbl[pi] : table[first_page + pi];
@@ -569,20 +579,21 @@ prefill_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap kmap, const __gr
   const int kv_end_all = max(kv_end[0], kv_end[1]);
   const int* table = block_table + static_cast<size_t>(row) * table_stride;
 
-  if (warp == 0) {
+  if (warp == 0 || warp >= 10) {
     // ---- copies, as in the kernel above
+    const int cw = warp == 0 ? 0 : warp - 9;
     bool ok = true;
     int* tbl = reinterpret_cast<int*>(sm + PAIR_TBL_OFF);
     const int first_page = k_begin / page_size;
     const int n_pages = min(TBL_ENTRIES, (kv_end_all + page_size - 1) / page_size - first_page);
-    for (int t = lane; t < n_pages; t += 32) tbl[t] = table[first_page + t];
-    __syncwarp();
+    for (int t = cw * 32 + lane; t < n_pages; t += 32 * PAIR_COPY_WARPS) tbl[t] = table[first_page + t];
+    asm volatile("bar.sync 1, %0;\n" ::"n"(32 * PAIR_COPY_WARPS) : "memory");      // (the copy warps only)
     auto fetch = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int first_key) {
       const int n_sub = (min(BKV, kv_end_all - first_key) + box_rows - 1) / box_rows;
       proxy_fence();
-      if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * box_rows * 128u);
+      if (cw == 0 && lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(n_sub) * 2u * box_rows * 128u);
       __syncwarp();
-      for (int j = lane; j < n_sub; j += 32) {
+      for (int j = cw + PAIR_COPY_WARPS * lane; j < n_sub; j += 32 * PAIR_COPY_WARPS) {
         const int key0 = first_key + j * box_rows;
         const int pi = key0 / page_size - first_page;
         const int page = pi < TBL_ENTRIES ? tbl[pi] : table[first_page + pi];
