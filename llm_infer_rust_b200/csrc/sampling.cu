@@ -60,9 +60,19 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 
 __device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx* sh, int begin = 0) {
   MaxIdx best = {-INFINITY, 0x7fffffff};
-  for (int i = begin + threadIdx.x; i < vocab; i += blockDim.x) {
+  // four logits a load where the row allows it (its start and `begin` on 16-byte steps), the rest one by one
+  const bool wide = reinterpret_cast<uintptr_t>(row) % 16 == 0 && begin % 4 == 0;
+  const int wide_end = wide ? begin + (vocab - begin) / 4 * 4 : begin;
+  for (int i = begin + 4 * threadIdx.x; i < wide_end; i += 4 * blockDim.x) {
+    const float4 v4 = *reinterpret_cast<const float4*>(row + i);
+    const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (!(v[e] != v[e])) best = better(best, MaxIdx{v[e], i + e});   // NaN never wins
+  }
+  for (int i = wide_end + threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = row[i];
-    if (!(v != v)) best = better(best, MaxIdx{v, i});             // NaN never wins
+    if (!(v != v)) best = better(best, MaxIdx{v, i});
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
