@@ -199,6 +199,55 @@ def test_decode_graphs_of_every_bucket_against_the_plain_implementation(name, ti
     assert engine.cache.manager.check() == ""
 
 
+@pytest.mark.parametrize("name", ["A", "B", "E"])
+def test_the_streaming_kernel_in_every_place_it_fits(name, tiny, tiny_weights, tmp_path, monkeypatch):
+    """The rule of sizes sends only the largest weights to the streaming kernel (csrc/stream_linear.cu), which no tiny
+    model has.  With the rule's size set to nothing, every few-row product that fits goes there (output projection,
+    gate/up, down projection, head; behind a norm, handing the next norm to the ring kernel's QKV, with 9 to 16 rows
+    and rows of x fetched beside the weights): decoded tokens in batches of 1 to 12 rows, eager and as graphs, against
+    the plain implementation."""
+    from llm_infer_rust_b200.engine import Engine, StepEntry
+    from llm_infer_rust_b200.kernels import ops
+    monkeypatch.setattr(ops, "stream_min_bytes", 0)
+    streamed, real = [0], ops.stream_linear
+
+    def counting(*args, **kwargs):
+        streamed[0] += 1
+        return real(*args, **kwargs)
+    monkeypatch.setattr(ops, "stream_linear", counting)
+    raw, page = tiny[name]["raw"], tiny[name]["page_size"]
+    vocab = raw["vocab_size"]
+    for graphs in (0, 4):
+        engine = Engine(folder_for(tiny, name, "bfloat16", tmp_path), dtype="bfloat16", max_running_req=12, page_size=page,
+                        max_total_tokens=2048, cuda_graph_bs=graphs, max_prefill_tokens_per_batch=0, chunked_prefill_size=0)
+        before = ops.launch_count()
+        uid = 0
+        for rows in (1, 3, 12):
+            seqs = {}
+            for _ in range(rows):
+                uid += 1
+                seqs[uid] = tokens(vocab, 21 + 5 * (uid % 4), 900 + uid)
+            decoded = 6
+            got = {r: [] for r in seqs}
+            for r, ids in seqs.items():
+                engine.open_request(r)
+                n = len(ids) - decoded
+                got[r].append(engine.step([StepEntry(r, ids[:n], list(range(n)))]).float().cpu().numpy())
+            for k in range(decoded):
+                logits = engine.step([StepEntry(r, [ids[len(ids) - decoded + k]], [0]) for r, ids in seqs.items()])
+                logits = logits.float().cpu().numpy()
+                for i, r in enumerate(seqs):
+                    got[r].append(logits[i:i + 1])
+            engine.check_kernel_errors()
+            for r, ids in seqs.items():
+                check(np.concatenate(got[r]), oracle(tiny_weights[name], raw, ids, "bfloat16"), "bfloat16",
+                      f"{rows} rows, graphs {graphs}, request {r}")
+                engine.close_request(r)
+        assert ops.launch_count() > before and engine.cache.manager.check() == ""
+        del engine
+    assert streamed[0] > 0                                     # (the rule did route there)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_weights_drawn_on_the_device_are_the_folder_s_weights(dtype, tiny, tmp_path):
     """``Engine(None, random_weights_config=...)`` (the constructor of the benchmark) draws on the device what
