@@ -18,7 +18,10 @@
 //             bytes on their way.  Asking for a smaller carve-out brought the speed back and cost a reconfiguration of
 //             every SM at both ends of the kernel, which ate the gain.  Copies into shared memory need no cache.)
 //   x         the rows of x' (at most 16) wait in shared memory, as in skinny_linear.cu: ONE CTA an SM stages them
-//             once and then walks over many tiles of weight rows.
+//             once and then walks over many tiles of weight rows.  Where the grid fills the GPU the CTAs are launched
+//             as clusters of two that stage half of the rows each and store them into both CTAs' shared memory:
+//             else 148 CTAs read the same rows of x and of the residual out of the second-level cache at the same
+//             moment (3.9 us of a 38 us launch at the Qwen3-8B gate/up; a decode step of 36 layers 3.92 -> 3.84 ms).
 //   split     the CTA's warps are G groups of KS warps.  A group owns a tile of RW x 16 weight rows at a time
 //             (SwiGLU: 8 or 16 gate rows and the same up rows); its KS warps split K (warp s takes the chunks
 //             [s C / KS, (s+1) C / KS)), leave their sums in shared memory, and the group's epilogue adds them in
@@ -73,6 +76,7 @@ struct StreamParams {
   int rw, ks;
   int groups, tiles;        // (filled by the launcher: groups of KS warps a CTA, tiles of the product)
   int xd;                   // the rows of x come with the weights' copies instead of waiting in shared memory: 1 yes, 0 no, -1 where they do not fit
+  int pair;                 // CTAs are launched as clusters of two that stage half of the rows of x each (1 yes, 0 no, -1 the launcher's choice)
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -106,6 +110,22 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 template <int NB> struct Layout { static constexpr int LDR = NB * 8 + 2; };
 __host__ __device__ inline int xs_row_bytes(int k) { return (2 * k) % 128 == 0 ? 2 * k + 64 : 2 * k; }
 
+// Shared memory of the other CTA of a cluster of two.
+__device__ __forceinline__ uint32_t peer_address(const void* p, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void store_peer16(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void store_peer_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void group_barrier(int group, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(threads) : "memory");
 }
@@ -242,9 +262,15 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
   // ---- the rows of x' into shared memory, four rows at a time: a thread takes 16 bytes of each of them (their loads
   // are on their way together), so a row's sum of squares is spread over the threads and meets in `part`
   if (!XD) {
-    const bool writer = NORM && blockIdx.x == 0 && p.residual_out != nullptr;
+    // A cluster of two CTAs stages half of the rows each and stores them into both CTAs' shared memory: every CTA
+    // else reads all rows of x and of the residual, 148 times the same 128 KB out of the second-level cache at once.
+    const int csize = p.pair ? 2 : 1;
+    uint32_t crank = 0;
+    if (p.pair) asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(crank));
+    const uint32_t peer_xs = p.pair ? peer_address(xs, crank ^ 1u) : 0u;
+    const bool writer = NORM && static_cast<int>(blockIdx.x) < csize && p.residual_out != nullptr;
 #pragma unroll 1
-    for (int m0 = 0; m0 < MP; m0 += 4) {
+    for (int m0 = 4 * static_cast<int>(crank); m0 < MP; m0 += 4 * csize) {
       float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       unsigned src[4];
 #pragma unroll
@@ -289,7 +315,10 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
           }
         }
 #pragma unroll
-        for (int r = 0; r < 4; ++r) *reinterpret_cast<uint4*>(xs + (m0 + r) * row_bytes + 2 * k) = xa[r];   // (rows beyond M: zeros)
+        for (int r = 0; r < 4; ++r) {
+          *reinterpret_cast<uint4*>(xs + (m0 + r) * row_bytes + 2 * k) = xa[r];   // (rows beyond M: zeros)
+          if (p.pair) store_peer16(peer_xs + (m0 + r) * row_bytes + 2 * k, xa[r]);
+        }
       }
       if (NORM) {
 #pragma unroll
@@ -301,13 +330,19 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
     }
     __syncthreads();
     if (NORM) {
-      if (threadIdx.x < MP) {
+      // (a CTA of a pair has the sums of its own rows only: it gives their scales to the other one too)
+      if (threadIdx.x < MP && (threadIdx.x >> 2) % csize == static_cast<int>(crank)) {
         float v = 0.0f;
         for (int w = 0; w < KS * G; ++w) v += part[w * MMAX + threadIdx.x];
-        scale[threadIdx.x] = rsqrtf(v / static_cast<float>(K) + p.eps);
+        const float sc = rsqrtf(v / static_cast<float>(K) + p.eps);
+        scale[threadIdx.x] = sc;
+        if (p.pair) store_peer_f32(peer_address(scale + threadIdx.x, crank ^ 1u), sc);
       }
-      __syncthreads();
     }
+    if (p.pair) cluster_barrier();    // (every thread of both CTAs: the other CTA's rows and scales have landed)
+    else if (NORM) __syncthreads();
+  } else if (p.pair) {
+    cluster_barrier();                // (not reached: pairs are launched with staged rows only)
   }
 
   // ---- the tiles of this group
@@ -528,8 +563,12 @@ B200_EXPORT int b200_stream_linear(const void* params, int sm_count, cudaStream_
     done = true;
   }
   const int sms = sm_count > 0 ? sm_count : 148;
-  const int ctas = (p.tiles + groups - 1) / groups < sms ? (p.tiles + groups - 1) / groups : sms;
-  return b200_launch(kernel, dim3(ctas), dim3(ks * groups * 32), smem, stream, 0, p);
+  int ctas = (p.tiles + groups - 1) / groups < sms ? (p.tiles + groups - 1) / groups : sms;
+  // pairs where the grid fills the machine (every CTA then reads all rows of x at the same moment) and has them staged
+  const bool pair = !xd && ctas >= 2 && (p.pair > 0 || (p.pair < 0 && ctas >= sms - 1));
+  if (pair) ctas &= ~1;
+  p.pair = pair ? 1 : 0;
+  return b200_launch(kernel, dim3(ctas), dim3(ks * groups * 32), smem, stream, pair ? 2 : 0, p);
 }
 
 B200_EXPORT int b200_stream_params_size() { return static_cast<int>(sizeof(StreamParams)); }

@@ -638,7 +638,7 @@ class _StreamParams(ctypes.Structure):
                 ("K", ctypes.c_int), ("mode", ctypes.c_int), ("out", ctypes.c_void_p),
                 ("post_residual", ctypes.c_void_p), ("post_sum_out", ctypes.c_void_p), ("post_stats", ctypes.c_void_p),
                 ("rw", ctypes.c_int), ("ks", ctypes.c_int), ("groups", ctypes.c_int), ("tiles", ctypes.c_int),
-                ("xd", ctypes.c_int)]
+                ("xd", ctypes.c_int), ("pair", ctypes.c_int)]
 
 
 def _stream_lib():
@@ -657,6 +657,7 @@ def _stream_lib():
 # (gate/up and the head), 1.320 -> 1.308 ms at the Qwen3-0.6B sizes (the head); smaller matrices are faster on the
 # ring kernel (1.41 ms with the 0.6B gate/up here).
 stream_min_bytes = int(os.environ.get("LLM_INFER_B200_STREAM_MIN_BYTES", 64 << 20))
+stream_pair = int(os.environ.get("LLM_INFER_B200_STREAM_PAIR", -1))
 
 
 def stream_ok(rows: int, weight: torch.Tensor, act_dtype: torch.dtype, mode: int = EPI_PLAIN_BF16,
@@ -698,14 +699,15 @@ def stream_tile_cols(mode: int, m: int, n: int, k: int, norm: bool) -> int:
 
 def stream_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: Optional[torch.Tensor] = None,
                   out: Optional[torch.Tensor] = None, norm_after=None, rw: int = 0, ks: int = 0,
-                  xd: int = -1) -> torch.Tensor:
+                  xd: int = -1, pair: Optional[int] = None) -> torch.Tensor:
     """epilogue(prologue(x) . weight^T) for at most 16 rows and a large weight (csrc/stream_linear.cu).
 
     ``x``: a bfloat16 tensor [rows, K] or a ``PendingNorm`` (with or without a residual); ``mode``: EPI_PLAIN_BF16,
     EPI_PLAIN_F32 or EPI_SWIGLU; ``norm_after`` = (residual, sum_out, stats [tiles, 16]) as for ``skinny_linear``,
     with tiles = ceil(N / ``stream_tile_cols(...)``); ``rw``, ``ks``: the launch's shape (groups of 16 weight rows a
     tile: 1 or 2; warps that split K: up to 24), 0 for the launcher's choice; ``xd``: whether the rows of x come with
-    the weights' copies instead of waiting in shared memory (1, 0, or -1: where they do not fit; never behind a norm).
+    the weights' copies instead of waiting in shared memory (1, 0, or -1: where they do not fit; never behind a norm);
+    ``pair``: clusters of two CTAs that stage half of the rows of x each (1, 0, or -1: where the grid fills the GPU).
     """
     _flush_held()
     pending = x if isinstance(x, PendingNorm) else None
@@ -738,6 +740,7 @@ def stream_linear(x, weight: torch.Tensor, mode: int = EPI_PLAIN_BF16, x_rows: O
     if norm_after is not None:
         P.post_residual, P.post_sum_out, P.post_stats = (t.data_ptr() for t in norm_after)
     P.out, P.rw, P.ks, P.xd = out.data_ptr(), rw, ks, xd
+    P.pair = stream_pair if pair is None else pair
     rc = _stream_lib().b200_stream_linear(ctypes.byref(P), _sm_count(src.device), _stream())
     _ok(rc, "stream_linear")
     return out

@@ -60,7 +60,9 @@ def test_stream_product_plain(m, n, k, norm):
                                         rows=rows if gather else None, write_residual=not gather)
                 # without a norm also with the rows of x fetched beside the weights (as rows too long for shared memory are)
                 for xd in ((0, 1) if norm == "none" else (-1,)):
-                    got = o.stream_linear(src, w, mode, x_rows=rows if (gather and norm == "none") else None, rw=rw, ks=ks, xd=xd)
+                    # (every other shape also as clusters of two CTAs that stage half of the rows of x each)
+                    got = o.stream_linear(src, w, mode, x_rows=rows if (gather and norm == "none") else None, rw=rw, ks=ks, xd=xd,
+                                          pair=(rw + ks) % 2)
                     assert got.dtype == dtype and tuple(got.shape) == (m, n)
                     tol = 2e-3 * scale if dtype == torch.float32 else 2.0 ** -7 * scale
                     assert (got.float() - want).abs().max() <= tol, (mode, gather, rw, ks, xd)
@@ -110,7 +112,7 @@ def test_stream_product_swiglu(m, inter, k, with_norm):
     want = R.ref_silu_mul(_bf(gu).to(torch.bfloat16))
     for rw, ks in [(0, 0), (2, 8), (2, 3), (2, 24), (2, 1), (1, 8), (1, 5), (1, 24)]:
         src = o.PendingNorm(x, res, nw, 1e-6) if with_norm else x
-        got = o.stream_linear(src, w, o.EPI_SWIGLU, rw=rw, ks=ks, xd=-1 if with_norm else ks % 2)
+        got = o.stream_linear(src, w, o.EPI_SWIGLU, rw=rw, ks=ks, xd=-1 if with_norm else ks % 2, pair=(ks // 2) % 2)
         assert tuple(got.shape) == (m, inter)
         assert (got.float() - want.float()).abs().max() <= 2.0 ** -6 * max(1.0, float(want.float().abs().max())), (rw, ks)
     o.check_errors(torch.device(DEV))
