@@ -159,6 +159,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
   unsigned char* ring = reinterpret_cast<unsigned char*>(scale + MMAX) + threadIdx.x * 16;
   const unsigned piece_stride = blockDim.x * 16;
   pdl_launch_dependents();          // the kernel after this one may set itself up from now on (it waits before it reads)
+  // (a pair: both CTAs say that they run; waited for before the first store into the other one's shared memory)
+  if (p.pair) asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
 
   const int chunks = K / CHUNK;
   const int c_lo = static_cast<int>(static_cast<long long>(slice) * chunks / KS);
@@ -268,6 +270,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
     uint32_t crank = 0;
     if (p.pair) asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(crank));
     const uint32_t peer_xs = p.pair ? peer_address(xs, crank ^ 1u) : 0u;
+    if (p.pair) asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     const bool writer = NORM && static_cast<int>(blockIdx.x) < csize && p.residual_out != nullptr;
 #pragma unroll 1
     for (int m0 = 4 * static_cast<int>(crank); m0 < MP; m0 += 4 * csize) {
@@ -341,8 +344,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) stream_linear_kernel(const Str
     }
     if (p.pair) cluster_barrier();    // (every thread of both CTAs: the other CTA's rows and scales have landed)
     else if (NORM) __syncthreads();
-  } else if (p.pair) {
-    cluster_barrier();                // (not reached: pairs are launched with staged rows only)
+  } else if (p.pair) {                // (not reached: pairs are launched with staged rows only)
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
   }
 
   // ---- the tiles of this group
